@@ -1,0 +1,214 @@
+// extern "C" edge of the library: POD structs in, status code + message out. Exceptions never
+// cross this boundary (same convention as the reference's bindings/c_api.cpp:25-40).
+#include "b200q.h"
+#include "kernels/quant_dispatch.h"
+#include "ops/context.h"
+#include "ops/ops.h"
+#include <cstdio>
+#include <cstring>
+#include <exception>
+#include <memory>
+
+struct b200q_context {
+    std::unique_ptr<tts::CudaContext> gpu;
+};
+
+namespace {
+using namespace tts;
+void copy_error(char *error, size_t capacity, const char *message) {
+    if (error && capacity) std::snprintf(error, capacity, "%s", message);
+}
+template <class Body> int guarded(char *error, size_t capacity, Body &&body) {
+    try {
+        body();
+        if (error && capacity) error[0] = 0;
+        return 0;
+    } catch (const std::exception &e) {
+        copy_error(error, capacity, e.what());
+    } catch (...) {
+        copy_error(error, capacity, "unknown error");
+    }
+    return -1;
+}
+CudaContext &context_of(b200q_context *c) {
+    if (!c || !c->gpu) throw std::invalid_argument("null b200q context");
+    return *c->gpu;
+}
+Type type_of(int code) {
+    if (code < 0 || code > int(Type::F64)) throw std::invalid_argument("invalid type code");
+    return static_cast<Type>(code);
+}
+TensorView view_of(const b200q_tensor *t) {
+    if (!t || !t->data) return {};
+    return TensorView(t->data, t->rows, t->cols, type_of(t->type), t->stride, t->device);
+}
+RowScaledView scaled_of(const b200q_row_scaled *r) {
+    if (!r) throw std::invalid_argument("null row-scaled view");
+    RowScaledView v;
+    v.values = view_of(&r->values);
+    v.scales = view_of(&r->scales);
+    v.group_size = r->group_size;
+    v.rotation_size = r->rotation_size;
+    return v;
+}
+ops::Epilogue epilogue_of(const b200q_epilogue *e) {
+    ops::Epilogue out;
+    if (!e) return out;
+    out.bias = view_of(&e->bias);
+    out.residual = view_of(&e->residual);
+    out.residual_f32 = view_of(&e->residual_f32);
+    out.value_scale = e->value_scale;
+    out.output_scale = e->output_scale;
+    out.residual_scale = e->residual_scale;
+    out.alpha = e->alpha;
+    if (e->activation < 0 || e->activation > int(ops::Activation::Sigmoid)) throw std::invalid_argument("invalid activation");
+    out.activation = static_cast<ops::Activation>(e->activation);
+    return out;
+}
+void put_path(b200q_path *out, LinearPath p) {
+    if (out) *out = {int32_t(p.kind), p.tokens, p.channels, p.splits};
+}
+} // namespace
+
+extern "C" {
+const char *b200q_version(void) { return "b200q 0.1 sm_100a; quantization=int8,fp8,group_int8,group_fp8"; }
+
+int b200q_context_create(int32_t device, void *stream, void *workspace, size_t workspace_bytes,
+                         const char *quantization, b200q_context **out, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        if (!out) throw std::invalid_argument("null output handle");
+        auto mode = quantization_from_string(quantization ? quantization : "");
+        if (mode == Quantization::None) throw std::invalid_argument("quantization must be int8, fp8, group_int8 or group_fp8");
+        auto holder = std::make_unique<b200q_context>();
+        holder->gpu = std::make_unique<CudaContext>(device, mode, static_cast<cudaStream_t>(stream), workspace, workspace_bytes);
+        *out = holder.release();
+    });
+}
+void b200q_context_destroy(b200q_context *c) { delete c; }
+
+int b200q_row_quantize(b200q_context *c, const b200q_tensor *source, const b200q_row_scaled *destination,
+                       char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        ExecutionScope scope(context_of(c));
+        ops::quantize_rows(view_of(source), scaled_of(destination));
+    });
+}
+int b200q_quantized_norm(b200q_context *c, const b200q_tensor *residual, const b200q_tensor *update,
+                         const b200q_tensor *weight, const b200q_row_scaled *output, float epsilon, int32_t gemma,
+                         const b200q_tensor *update_scale, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        ExecutionScope scope(context_of(c));
+        ops::quantized_norm(view_of(residual), view_of(update), view_of(weight), scaled_of(output), epsilon,
+                            gemma != 0, view_of(update_scale));
+    });
+}
+int b200q_quantized_gated(b200q_context *c, const b200q_tensor *input, const b200q_row_scaled *output, int32_t kind,
+                          char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        ExecutionScope scope(context_of(c));
+        ops::quantized_gated(view_of(input), scaled_of(output), kind);
+    });
+}
+int b200q_prepare(b200q_context *c, int32_t rows, int32_t channels, int32_t reduction, int32_t output_type,
+                  int32_t activation_group, int32_t weight_group, b200q_path *chosen, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        auto &gpu = context_of(c);
+        ExecutionScope scope(gpu);
+        QuantizationGroups groups{activation_group, weight_group, 0};
+        gpu.quantization->prepare(rows, channels, reduction, type_of(output_type), groups);
+        put_path(chosen, gpu.quantization->planned_path(rows, channels, reduction, type_of(output_type), groups));
+    });
+}
+int b200q_seal(b200q_context *c, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        auto &gpu = context_of(c);
+        ExecutionScope scope(gpu);
+        ops::seal(gpu.device);
+    });
+}
+int b200q_linear(b200q_context *c, const b200q_row_scaled *input, const b200q_row_scaled *weight,
+                 const b200q_tensor *output, const b200q_epilogue *epilogue, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        auto &gpu = context_of(c);
+        ExecutionScope scope(gpu);
+        if (!epilogue) {
+            ops::matmul(scaled_of(input), scaled_of(weight), view_of(output));
+            return;
+        }
+        auto e = epilogue_of(epilogue);
+        if (!gpu.quantization->linear_finish(scaled_of(input), scaled_of(weight), view_of(output), e))
+            throw std::invalid_argument("epilogue cannot be fused, or the shape was not prepared");
+    });
+}
+int b200q_quant_linear(b200q_context *c, const b200q_path *path, const b200q_row_scaled *input,
+                       const b200q_row_scaled *weight, const b200q_tensor *output, const b200q_epilogue *epilogue,
+                       char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        auto &gpu = context_of(c);
+        ExecutionScope scope(gpu);
+        if (!path) throw std::invalid_argument("null path");
+        auto x = scaled_of(input), w = scaled_of(weight);
+        auto y = view_of(output);
+        x.validate();
+        w.validate();
+        if (x.values.type != w.values.type || x.values.cols != w.values.cols || x.rotation_size != w.rotation_size ||
+            y.rows != x.values.rows || y.cols != w.values.rows || !y.dense() || !y.data)
+            throw std::invalid_argument("quantized linear dimensions/type mismatch");
+        for (const TensorView *v : {&x.values, &x.scales, &w.values, &w.scales, &y})
+            if (v->device != gpu.device) throw std::invalid_argument("operand is not on the context's device");
+        ops::Epilogue e = epilogue_of(epilogue);
+        launch_quant_linear({static_cast<LinearKind>(path->kind), path->tokens, path->channels, path->splits},
+                            {y.rows, y.cols, x.values.cols, x.group_size, w.group_size}, x.values.data,
+                            x.scales.ptr<float>(), w.values.data, w.scales.ptr<float>(), y.data,
+                            gpu.gemm_workspace.data(), gpu.gemm_workspace.size(), gpu.stream, x.values.type, y.type,
+                            epilogue ? &e : nullptr);
+    });
+}
+int b200q_select_path(b200q_context *c, int32_t rows, int32_t channels, int32_t reduction, int32_t activation_group,
+                      int32_t weight_group, b200q_path *chosen, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        auto &gpu = context_of(c);
+        put_path(chosen, select_tcgen05_path({rows, channels, reduction, activation_group, weight_group},
+                                             quantized_type(gpu.mode), gpu.multiprocessors, gpu.gemm_workspace.size()));
+    });
+}
+int b200q_linear_forward(b200q_context *c, const b200q_tensor *input, const b200q_row_scaled *weight,
+                         const b200q_row_scaled *scratch, const b200q_tensor *output, const b200q_epilogue *epilogue,
+                         char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        ExecutionScope scope(context_of(c));
+        ops::Epilogue e = epilogue_of(epilogue);
+        TensorView bias = e.bias;
+        e.bias = {};
+        ops::linear(view_of(input), scaled_of(weight), bias, view_of(output), e, scaled_of(scratch));
+    });
+}
+int b200q_status(b200q_context *c, int32_t *status, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        auto &gpu = context_of(c);
+        ExecutionScope scope(gpu);
+        int value = gpu.quantization->status();
+        if (status) *status = value;
+    });
+}
+int b200q_multiprocessors(b200q_context *c) { return c && c->gpu ? c->gpu->multiprocessors : 0; }
+int32_t b200q_row_capacity(int32_t rows, uint32_t bins_per_octave) {
+    try {
+        return row_capacity(rows, bins_per_octave);
+    } catch (...) {
+        return -1;
+    }
+}
+int b200q_plan_path(int32_t rows, int32_t channels, int32_t reduction, int32_t activation_group, int32_t weight_group,
+                    int32_t format, int32_t multiprocessors, size_t workspace_bytes, b200q_path *chosen,
+                    size_t *workspace_needed, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        if (rows < 1 || channels < 1 || reduction < 1 || reduction % 16 || channels % 16)
+            throw std::invalid_argument("quantized GEMM unsupported shape");
+        KernelProblem problem{rows, channels, reduction, activation_group, weight_group};
+        LinearPath path = select_tcgen05_path(problem, type_of(format), multiprocessors, workspace_bytes);
+        put_path(chosen, path);
+        if (workspace_needed) *workspace_needed = quant_linear_workspace_bytes(path, problem);
+    });
+}
+}

@@ -1,0 +1,35 @@
+// Host launchers of the quantized GEMM. Signatures follow the reference's
+// (src/ops/kernels/quant/quant_dispatch.h:7-17) so `QuantizedGemm` and any direct caller can
+// switch without edits; `LinearKind::Tcgen05` is the only kind this build executes.
+#pragma once
+#include "core/quantization.h"
+#include <cuda_runtime.h>
+
+namespace tts {
+namespace ops { struct Epilogue; }
+
+void grouped_quant_gemm(KernelProblem, const void *input, const float *input_scales,
+                        const void *weights, const float *weight_scales, void *output,
+                        cudaStream_t, Type format, Type output_type, int tokens = 16, int splits = 1,
+                        void *workspace = nullptr, size_t workspace_bytes = 0);
+void launch_quant_linear(LinearPath config, KernelProblem shape, const void *input,
+                         const float *input_scales, const void *weights, const float *weight_scales,
+                         void *output, void *workspace, size_t workspace_bytes, cudaStream_t stream,
+                         Type format = Type::FP8, Type output_type = Type::BF16,
+                         const ops::Epilogue *finish = nullptr);
+// Initialization only; the fused finish needs no extra resources on this path.
+KernelResources quant_linear_finish_resources(LinearPath, Type format, Type output_type);
+
+// --- additions of this build -------------------------------------------------------------------
+// Tile/split choice for a problem: tokens = token tile (16..256), channels = 128, splits = split-K.
+LinearPath select_tcgen05_path(KernelProblem, Type format, int multiprocessors, size_t workspace_bytes);
+// Bytes of caller workspace a path needs (header + split-K partials).
+size_t quant_linear_workspace_bytes(LinearPath, KernelProblem);
+// One-time set-up per device and process: raises the dynamic shared-memory limit of every kernel
+// instance and resolves the driver entry point for tensor maps. Call before stream capture.
+void quant_linear_initialize(int device);
+// Zeroes the ticket/status header of a fresh workspace (asynchronously on `stream`).
+void quant_linear_reset_workspace(void *workspace, size_t workspace_bytes, cudaStream_t stream);
+// Blocking read of the status word: 0 = clean, otherwise 1 + index of the tile whose bounded wait gave up.
+int quant_linear_status(const void *workspace, cudaStream_t stream);
+} // namespace tts

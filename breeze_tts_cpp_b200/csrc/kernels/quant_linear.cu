@@ -1,0 +1,276 @@
+// Host side of the sm_100a quantized GEMM: tensor-map construction, tile/split selection and the
+// launch. Drop-in for the reference launchers `launch_quant_linear` and `grouped_quant_gemm`
+// (src/ops/kernels/quant/quant_dispatch.cu:194-234, quant_grouped.cu:221-239).
+#include "kernels/quant_dispatch.h"
+#include "kernels/quant_linear_sm100.cuh"
+#include "ops/epilogue.h"
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <map>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <tuple>
+
+namespace tts {
+namespace {
+using namespace b200;
+constexpr size_t kSmemBudget = 226 * 1024; // dynamic part; the kernel adds ~0.3 KB of static barriers (227 KB per CTA is the limit)
+
+void check(cudaError_t status, const char *what) {
+    if (status != cudaSuccess)
+        throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(status));
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_tiled() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
+        void *entry = nullptr;
+        cudaDriverEntryPointQueryResult result{};
+        check(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result),
+              "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+        if (!entry || result != cudaDriverEntryPointSuccess)
+            throw std::runtime_error("cuTensorMapEncodeTiled is unavailable in this driver");
+        return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(entry);
+    }();
+    return fn;
+}
+
+// Row-major one-byte matrix [rows, k]; box = 128 bytes of K by `box_rows` rows, 128B swizzle,
+// out-of-range rows/columns read as zero (so ragged M, N and K tails need no special code).
+const CUtensorMap &tensor_map(const void *base, int rows, int k, int box_rows, bool weights) {
+    using Key = std::tuple<const void *, int, int, int>;
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex guard;
+    std::lock_guard<std::mutex> lock(guard);
+    Key key{base, rows, k, box_rows};
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    if (reinterpret_cast<uintptr_t>(base) % 16 || k % 16)
+        throw std::invalid_argument("quantized operand must be 16-byte aligned with K a multiple of 16");
+    CUtensorMap map;
+    cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(rows)};
+    cuuint64_t strides[1] = {cuuint64_t(k)};
+    cuuint32_t box[2] = {cuuint32_t(kBlockK), cuuint32_t(box_rows)};
+    cuuint32_t element_strides[2] = {1, 1};
+    CUresult status = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims,
+                                     strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                     CU_TENSOR_MAP_SWIZZLE_128B,
+                                     weights ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (status != CUDA_SUCCESS)
+        throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(status)));
+    if (cache.size() > 4096) cache.clear();
+    return cache.emplace(key, map).first->second;
+}
+
+template <Type F, bool Grouped, int BN> auto kernel_of() { return w8a8_tcgen05_gemm<F, Grouped, BN>; }
+
+struct Shape {
+    int stages;
+    size_t smem;
+};
+Shape shape_for(int bn, bool grouped, int kb_per_split) {
+    size_t stage = size_t(kBlockChannels + bn) * kBlockK;
+    size_t scales = grouped ? size_t(kb_per_split) * (bn + kBlockChannels) * sizeof(float) : 0;
+    if (1024 + scales + 2 * stage > kSmemBudget)
+        throw std::invalid_argument("quantized GEMM: K-group scales of one split exceed shared memory; use more splits");
+    int stages = int((kSmemBudget - 1024 - scales) / stage);
+    stages = std::max(2, std::min({stages, kMaxStages, std::max(2, kb_per_split)}));
+    return {stages, 1024 + scales + size_t(stages) * stage};
+}
+
+template <Type F, bool Grouped, int BN>
+void launch_instance(const CUtensorMap &map_w, const CUtensorMap &map_x, const GemmArgs &args, dim3 grid,
+                     size_t smem, cudaStream_t stream) {
+    w8a8_tcgen05_gemm<F, Grouped, BN><<<grid, kGemmThreads, smem, stream>>>(map_w, map_x, args);
+}
+template <Type F, bool Grouped>
+void launch_tokens(int bn, const CUtensorMap &map_w, const CUtensorMap &map_x, const GemmArgs &args, dim3 grid,
+                   size_t smem, cudaStream_t stream) {
+    switch (bn) {
+    case 16: launch_instance<F, Grouped, 16>(map_w, map_x, args, grid, smem, stream); break;
+    case 32: launch_instance<F, Grouped, 32>(map_w, map_x, args, grid, smem, stream); break;
+    case 64: launch_instance<F, Grouped, 64>(map_w, map_x, args, grid, smem, stream); break;
+    case 128: launch_instance<F, Grouped, 128>(map_w, map_x, args, grid, smem, stream); break;
+    case 256:
+        if constexpr (!Grouped) { launch_instance<F, false, 256>(map_w, map_x, args, grid, smem, stream); break; }
+        [[fallthrough]];
+    default: throw std::invalid_argument("unsupported token tile for the tcgen05 GEMM");
+    }
+}
+
+template <Type F, bool Grouped, int BN> void raise_limit() {
+    check(cudaFuncSetAttribute(w8a8_tcgen05_gemm<F, Grouped, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               int(kSmemBudget)),
+          "cudaFuncSetAttribute(shared memory)");
+}
+template <Type F> void raise_limits() {
+    raise_limit<F, false, 16>(); raise_limit<F, false, 32>(); raise_limit<F, false, 64>();
+    raise_limit<F, false, 128>(); raise_limit<F, false, 256>();
+    raise_limit<F, true, 16>(); raise_limit<F, true, 32>(); raise_limit<F, true, 64>(); raise_limit<F, true, 128>();
+}
+} // namespace
+
+void quant_linear_initialize(int device) {
+    static std::mutex guard;
+    static std::map<int, bool> done;
+    std::lock_guard<std::mutex> lock(guard);
+    if (done[device]) return;
+    int current = 0;
+    check(cudaGetDevice(&current), "cudaGetDevice");
+    check(cudaSetDevice(device), "cudaSetDevice");
+    cudaDeviceProp p{};
+    check(cudaGetDeviceProperties(&p, device), "cudaGetDeviceProperties");
+    if (p.major != 10)
+        throw std::runtime_error("this library only carries sm_100a kernels; device is sm_" +
+                                 std::to_string(p.major) + std::to_string(p.minor));
+    raise_limits<Type::I8>();
+    raise_limits<Type::FP8>();
+    encode_tiled();
+    check(cudaSetDevice(current), "cudaSetDevice");
+    done[device] = true;
+}
+
+void quant_linear_reset_workspace(void *workspace, size_t bytes, cudaStream_t stream) {
+    if (!workspace || bytes < kWorkspaceHeader) throw std::invalid_argument("GEMM workspace is smaller than its header");
+    check(cudaMemsetAsync(workspace, 0, kWorkspaceHeader, stream), "cudaMemsetAsync(workspace header)");
+}
+
+int quant_linear_status(const void *workspace, cudaStream_t stream) {
+    int status = 0;
+    check(cudaMemcpyAsync(&status, static_cast<const char *>(workspace) + kStatusOffset, sizeof(int),
+                          cudaMemcpyDeviceToHost, stream),
+          "cudaMemcpyAsync(status)");
+    check(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+    return status;
+}
+
+size_t quant_linear_workspace_bytes(LinearPath path, KernelProblem p) {
+    if (path.splits <= 1) return kWorkspaceHeader;
+    size_t tiles = size_t((p.channels + kBlockChannels - 1) / kBlockChannels) * ((p.rows + path.tokens - 1) / path.tokens);
+    return kWorkspaceHeader + tiles * path.splits * path.tokens * kBlockChannels * sizeof(float);
+}
+
+LinearPath select_tcgen05_path(KernelProblem p, Type format, int sms, size_t workspace_bytes) {
+    (void)format;
+    if (sms <= 0) sms = 148;
+    const bool grouped = p.input_group || p.weight_group;
+    const int max_tokens = grouped ? 128 : 256;
+    int bn = 16;
+    while (bn < max_tokens && bn < p.rows) bn *= 2;
+    const int n_tiles = (p.channels + kBlockChannels - 1) / kBlockChannels;
+    const int m_tiles = (p.rows + bn - 1) / bn;
+    const int64_t tiles = int64_t(n_tiles) * m_tiles;
+    const int kb_total = (p.reduction + kBlockK - 1) / kBlockK;
+    LinearPath best{LinearKind::Tcgen05, bn, kBlockChannels, 1};
+    if (tiles > 4096) return best; // ticket table bound; such grids fill the machine anyway
+    // Cost in "K blocks streamed by the busiest SM", plus a fixed per-CTA prologue/epilogue and
+    // the split reduction. Memory-bound shapes want every SM to stream a disjoint weight slab.
+    double best_cost = 1e300;
+    for (int splits = 1; splits <= std::min(kb_total, 32); ++splits) {
+        LinearPath candidate{LinearKind::Tcgen05, bn, kBlockChannels, splits};
+        if (quant_linear_workspace_bytes(candidate, p) > workspace_bytes) break;
+        if (grouped) {
+            int per_split = (kb_total + splits - 1) / splits;
+            if (1024 + size_t(per_split) * (bn + kBlockChannels) * 4 + 2 * size_t(kBlockChannels + bn) * kBlockK > kSmemBudget)
+                continue;
+        }
+        int64_t ctas = tiles * splits;
+        double waves = double((ctas + sms - 1) / sms);
+        double per_cta = double((kb_total + splits - 1) / splits) + 6.0 + (splits > 1 ? 2.0 + 0.25 * splits * bn / 16.0 : 0.0);
+        double cost = waves * per_cta;
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best = candidate;
+        }
+    }
+    return best;
+}
+
+void launch_quant_linear(LinearPath config, KernelProblem shape, const void *input, const float *xs,
+                         const void *weights, const float *ws, void *y, void *workspace, size_t bytes,
+                         cudaStream_t stream, Type format, Type output_type, const ops::Epilogue *finish) {
+    const bool grouped = shape.input_group || shape.weight_group;
+    if (output_type != Type::BF16 && output_type != Type::F16 &&
+        !(output_type == Type::I32 && format == Type::I8 && !grouped && !finish))
+        throw std::invalid_argument("quantized GEMM output must be F16 or BF16");
+    if (format != Type::I8 && format != Type::FP8) throw std::invalid_argument("unsupported quantized storage type");
+    if (config.kind != LinearKind::Tcgen05)
+        throw std::invalid_argument("this build executes LinearKind::Tcgen05 paths only");
+    if (shape.rows < 1 || shape.channels < 1 || shape.reduction < 1 || shape.reduction % 16 || shape.channels % 16)
+        throw std::invalid_argument("quantized GEMM unsupported shape");
+    if (format == Type::I8 && shape.reduction > INT32_MAX / (128 * 128))
+        throw std::invalid_argument("INT8 reduction can overflow INT32");
+    if ((shape.input_group && shape.input_group != kBlockK) || (shape.weight_group && shape.weight_group != kBlockK))
+        throw std::invalid_argument("the tcgen05 GEMM supports K groups of 128 only");
+    if (!input || !xs || !weights || !ws || !y) throw std::invalid_argument("quantized GEMM null operand");
+    const int kb_total = (shape.reduction + kBlockK - 1) / kBlockK;
+    const int bn = config.tokens, splits = config.splits;
+    if (config.channels != kBlockChannels || splits < 1 || splits > kb_total)
+        throw std::invalid_argument("invalid tcgen05 tile or split");
+    const int n_tiles = (shape.channels + kBlockChannels - 1) / kBlockChannels, m_tiles = (shape.rows + bn - 1) / bn;
+    if (m_tiles > 65535 || splits > 65535) throw std::invalid_argument("quantized GEMM grid exceeds capacity");
+    if (!workspace || bytes < kWorkspaceHeader) throw std::invalid_argument("quantized GEMM workspace missing");
+    if (splits > 1) {
+        if (size_t(n_tiles) * m_tiles > kTicketBytes / sizeof(int))
+            throw std::invalid_argument("too many tiles for split-K tickets");
+        if (quant_linear_workspace_bytes(config, shape) > bytes)
+            throw std::invalid_argument("quantized GEMM partial workspace overflow");
+    }
+
+    GemmArgs args{};
+    args.m = shape.rows; args.n = shape.channels; args.k = shape.reduction;
+    args.sx = xs; args.sw = ws; args.out = y; args.out_type = int(output_type);
+    args.input_group = shape.input_group; args.weight_group = shape.weight_group;
+    args.splits = splits;
+    char *base = static_cast<char *>(workspace);
+    args.tickets = reinterpret_cast<int *>(base);
+    args.status = reinterpret_cast<int *>(base + kStatusOffset);
+    args.partials = reinterpret_cast<float *>(base + kWorkspaceHeader);
+    if (finish) {
+        const auto &e = *finish;
+        if (!ops::fusable(e)) throw std::invalid_argument("unsupported quantized native Finish path");
+        auto same_type = [&](const TensorView &v) { return !v.data || v.type == output_type; };
+        if (!same_type(e.bias) || !same_type(e.residual) ||
+            (e.bias.data && e.bias.numel() != size_t(shape.channels)) ||
+            (e.residual.data && (e.residual.rows != shape.rows || e.residual.cols != shape.channels)) ||
+            (e.residual_f32.data && (e.residual_f32.type != Type::F32 || !e.residual_f32.dense() ||
+                                     e.residual_f32.rows != shape.rows || e.residual_f32.cols != shape.channels)))
+            throw std::invalid_argument("quantized linear finish operand mismatch");
+        args.ep.bias = e.bias.data;
+        args.ep.residual = e.residual.data;
+        args.ep.residual_ld = e.residual.data ? e.residual.ld() : 0;
+        args.ep.residual_f32 = e.residual_f32.ptr<const float>();
+        args.ep.value_scale = e.value_scale; args.ep.residual_scale = e.residual_scale;
+        args.ep.output_scale = e.output_scale; args.ep.alpha = e.alpha;
+        args.ep.activation = int(e.activation);
+        args.ep.chain = e.bias.data || e.residual.data || e.value_scale != 1.f || e.output_scale != 1.f ||
+                        e.activation != ops::Activation::Identity;
+    }
+    const Shape launch = shape_for(bn, grouped, (kb_total + splits - 1) / splits);
+    args.stages = launch.stages;
+    const CUtensorMap &map_w = tensor_map(weights, shape.channels, shape.reduction, kBlockChannels, true);
+    const CUtensorMap &map_x = tensor_map(input, shape.rows, shape.reduction, bn, false);
+    dim3 grid(n_tiles, m_tiles, splits);
+    if (format == Type::I8) {
+        if (grouped) launch_tokens<Type::I8, true>(bn, map_w, map_x, args, grid, launch.smem, stream);
+        else launch_tokens<Type::I8, false>(bn, map_w, map_x, args, grid, launch.smem, stream);
+    } else {
+        if (grouped) launch_tokens<Type::FP8, true>(bn, map_w, map_x, args, grid, launch.smem, stream);
+        else launch_tokens<Type::FP8, false>(bn, map_w, map_x, args, grid, launch.smem, stream);
+    }
+    check(cudaGetLastError(), "quantized GEMM launch");
+}
+
+void grouped_quant_gemm(KernelProblem problem, const void *input, const float *input_scales,
+                        const void *weights, const float *weight_scales, void *output, cudaStream_t stream,
+                        Type format, Type output_type, int tokens, int splits, void *workspace,
+                        size_t workspace_bytes) {
+    if (!problem.input_group && !problem.weight_group)
+        throw std::invalid_argument("group scales require a grouped GEMM implementation");
+    launch_quant_linear({LinearKind::Tcgen05, tokens, kBlockChannels, splits}, problem, input, input_scales, weights,
+                        weight_scales, output, workspace, workspace_bytes, stream, format, output_type, nullptr);
+}
+
+KernelResources quant_linear_finish_resources(LinearPath, Type, Type) { return {}; }
+} // namespace tts

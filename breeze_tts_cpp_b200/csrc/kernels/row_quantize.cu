@@ -1,0 +1,135 @@
+// Stage 1 (and the stage-3 producer) of the quantized linear path: dynamic per-token quantization
+// of a 16-bit [rows,K] matrix to one-byte values plus fp32 scales, optionally after the matched
+// H128 rotation and optionally with K-group scales. One pass over HBM: each thread keeps its
+// 128-bit loads in registers across the amax reduction, so the row is read once and written once.
+//
+// Replaces the reference launcher `launch_row_quantize`
+// (src/ops/kernels/quant/row_quantize.cu:167-193) and the four kernels behind it
+// (:24-37 scalar, :42-87 register-cached, :90-115 rotated per-row, :145-165 K-group).
+#include "kernels/row_quantize.h"
+#include "kernels/quant_codec.cuh"
+#include <stdexcept>
+
+namespace tts {
+namespace b200 {
+namespace {
+constexpr int kThreads = 256;
+
+// Register-resident rows: K <= Items * 2048 * parts.
+template <Type F, class T, int Items, bool Rotate>
+__global__ void __launch_bounds__(kThreads)
+row_quantize_cached(const T *__restrict__ x, unsigned char *__restrict__ q, float *__restrict__ scales,
+                    int rows, int cols, int stride, int group, int parts, bool aligned) {
+    __shared__ float slots[kThreads / 32];
+    const int row = blockIdx.x / parts, shard = blockIdx.x % parts;
+    const T *source = x + size_t(row) * stride;
+    float v[Items][8];
+#pragma unroll
+    for (int j = 0; j < Items; ++j) {
+        int column = ((j * parts + shard) * kThreads + int(threadIdx.x)) * 8;
+        if (column < cols) {
+            load8(source + column, cols - column, aligned, v[j]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
+        }
+    }
+    quantize_tail<F, kThreads, Items, Rotate>(v, q, scales, row, rows, cols, group, shard, parts,
+                                              aligned, slots);
+}
+
+// Arbitrarily wide rows with one scale per row: two passes over the row (the second one mostly
+// served by L2), the rotation recomputed rather than spilled.
+template <Type F, class T, bool Rotate>
+__global__ void __launch_bounds__(kThreads)
+row_quantize_wide(const T *__restrict__ x, unsigned char *__restrict__ q, float *__restrict__ scales,
+                  int cols, int stride, bool aligned) {
+    __shared__ float slots[kThreads / 32];
+    const int row = blockIdx.x;
+    const T *source = x + size_t(row) * stride;
+    const int padded = (cols + kThreads * 8 - 1) / (kThreads * 8) * (kThreads * 8);
+    float amax = 0.f, v[8];
+    for (int column = threadIdx.x * 8; column < padded; column += kThreads * 8) {
+        load8(source + (column < cols ? column : 0), column < cols ? cols - column : 0, aligned, v);
+        if (Rotate) hadamard128(v, column);
+        if (column < cols) amax = fmaxf(amax, abs_max8(v));
+    }
+    float step = quant_scale<F>(cta_max<kThreads>(amax, slots));
+    float inverse = __fdiv_rn(1.f, step);
+    if (!threadIdx.x) scales[row] = step;
+    for (int column = threadIdx.x * 8; column < padded; column += kThreads * 8) {
+        load8(source + (column < cols ? column : 0), column < cols ? cols - column : 0, aligned, v);
+        if (Rotate) hadamard128(v, column);
+        if (column < cols)
+            store8<F>(q + size_t(row) * cols + column, cols - column, aligned, v, inverse);
+    }
+}
+
+template <Type F, class T, bool Rotate>
+void launch_typed(const T *x, unsigned char *q, float *scales, int rows, int cols, int stride,
+                  int group, int multiprocessors, cudaStream_t stream) {
+    const bool aligned = cols % 8 == 0 && stride % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(q) % 8 == 0;
+    const int chunks = (cols + kThreads * 8 - 1) / (kThreads * 8); // 2048-column slabs per row
+    int parts = 1;
+    if (group) {
+        // K groups never cross a 2048-column slab, so slabs of one row can go to different CTAs.
+        // Spread short batches over the machine; long batches keep whole rows per CTA.
+        while (parts < chunks && int64_t(rows) * parts * 2 <= multiprocessors) parts *= 2;
+        if (chunks > 4 * parts) parts = (chunks + 3) / 4;
+    } else if (chunks > 4) {
+        row_quantize_wide<F, T, Rotate><<<rows, kThreads, 0, stream>>>(x, q, scales, cols, stride, aligned);
+        return;
+    }
+    const int items = (chunks + parts - 1) / parts;
+    const unsigned grid = unsigned(rows) * unsigned(parts);
+#define B200Q_LAUNCH(I)                                                                            \
+    row_quantize_cached<F, T, I, Rotate><<<grid, kThreads, 0, stream>>>(x, q, scales, rows, cols,   \
+                                                                        stride, group, parts, aligned)
+    switch (items) {
+    case 1: B200Q_LAUNCH(1); break;
+    case 2: B200Q_LAUNCH(2); break;
+    case 3: B200Q_LAUNCH(3); break;
+    default: B200Q_LAUNCH(4); break;
+    }
+#undef B200Q_LAUNCH
+}
+
+template <Type F, class T>
+void launch_rotation(const T *x, unsigned char *q, float *scales, int rows, int cols, int stride,
+                     int group, int rotation, int sms, cudaStream_t stream) {
+    if (rotation) launch_typed<F, T, true>(x, q, scales, rows, cols, stride, group, sms, stream);
+    else launch_typed<F, T, false>(x, q, scales, rows, cols, stride, group, sms, stream);
+}
+} // namespace
+} // namespace b200
+
+void launch_row_quantize(TensorView source, RowScaledView destination, cudaStream_t stream,
+                         int multiprocessors) {
+    destination.validate();
+    if ((source.type != Type::BF16 && source.type != Type::F16) || !source.data ||
+        !destination.values.data || !destination.scales.data || source.rows < 1 || source.cols < 1 ||
+        source.rows != destination.values.rows || source.cols != destination.values.cols)
+        throw std::invalid_argument("row quantization shape/type mismatch");
+    if (int64_t(source.rows) * ((source.cols + 2047) / 2048) > INT32_MAX)
+        throw std::invalid_argument("quantization grid exceeds capacity");
+    if (multiprocessors <= 0) multiprocessors = 148;
+    auto *q = destination.values.ptr<unsigned char>();
+    auto *s = destination.scales.ptr<float>();
+    const int rows = source.rows, cols = source.cols, ld = source.ld();
+    const int group = destination.group_size, rotation = destination.rotation_size;
+    const bool fp8 = destination.values.type == Type::FP8;
+    if (source.type == Type::F16) {
+        auto *x = source.ptr<const __half>();
+        if (fp8) b200::launch_rotation<Type::FP8>(x, q, s, rows, cols, ld, group, rotation, multiprocessors, stream);
+        else b200::launch_rotation<Type::I8>(x, q, s, rows, cols, ld, group, rotation, multiprocessors, stream);
+    } else {
+        auto *x = source.ptr<const __nv_bfloat16>();
+        if (fp8) b200::launch_rotation<Type::FP8>(x, q, s, rows, cols, ld, group, rotation, multiprocessors, stream);
+        else b200::launch_rotation<Type::I8>(x, q, s, rows, cols, ld, group, rotation, multiprocessors, stream);
+    }
+    cudaError_t status = cudaGetLastError();
+    if (status != cudaSuccess)
+        throw std::runtime_error(std::string("row quantize launch: ") + cudaGetErrorString(status));
+}
+} // namespace tts

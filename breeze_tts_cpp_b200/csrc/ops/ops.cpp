@@ -1,0 +1,83 @@
+#include "ops/ops.h"
+#include "ops/context.h"
+#include "kernels/row_quantize.h"
+#include "kernels/quant_norm.h"
+#include "kernels/quant_gated.h"
+
+namespace tts::ops {
+// reference: src/ops/basic.cpp:69-78
+void quantize_rows(TensorView input, RowScaledView output) {
+    output.validate();
+    if ((input.type != Type::BF16 && input.type != Type::F16) || input.rows < 1 || input.cols < 1 || !input.data ||
+        !output.values.data || !output.scales.data || input.rows != output.values.rows ||
+        input.cols != output.values.cols)
+        throw std::invalid_argument("quantization source/destination shape/type mismatch");
+    auto &gpu = execution_context(input, {output.values, output.scales});
+    launch_row_quantize(input, output, gpu.stream, gpu.multiprocessors);
+}
+// reference: src/ops/basic.cpp:64-67
+void matmul(RowScaledView input, RowScaledView weight, TensorView output) {
+    auto &gpu = execution_context(output, {input.values, input.scales, weight.values, weight.scales});
+    if (!gpu.quantization) throw std::logic_error("context was created without a quantization mode");
+    gpu.quantization->linear(input, weight, output);
+}
+// reference: src/ops/basic.cpp:48-53
+void prepare_quantized(TensorView weight, int rows, int output_channels, int input_channels, Type type,
+                       const Epilogue &epilogue, QuantizationGroups groups) {
+    auto &gpu = execution_context(weight);
+    if (!gpu.quantization) throw std::logic_error("context was created without a quantization mode");
+    gpu.quantization->prepare(rows, output_channels, input_channels, type, groups);
+    gpu.quantization->prepare_finish(rows, output_channels, input_channels, type, epilogue, groups);
+}
+// reference: src/ops/basic.cpp:54-58
+void quantized_norm(TensorView input, TensorView update, TensorView weight, RowScaledView output, float epsilon,
+                    bool gemma, TensorView scale) {
+    auto &gpu = execution_context(input, {update, weight, output.values, output.scales, scale});
+    launch_quantized_norm(input, update, weight, output, epsilon, gemma, scale, gpu.stream);
+}
+// reference: src/ops/basic.cpp:59-63
+void quantized_gated(TensorView input, RowScaledView output, int kind) {
+    auto &gpu = execution_context(input, {output.values, output.scales});
+    launch_quantized_gated(input, output, kind, gpu.stream, gpu.multiprocessors, gpu.quant_gated_clusters);
+}
+void seal(int device) {
+    auto &gpu = execution_context(device);
+    gpu.plans_sealed = true;
+    if (gpu.quantization) gpu.quantization->seal();
+}
+
+// reference: src/ops/linear.cpp:26-83, quantized-weight branch. The dense BF16 branch of the
+// reference is a different subsystem and is not provided here.
+void linear(const LinearOperand &input, const LinearOperand &weight, TensorView bias, TensorView output, Epilogue e,
+            RowScaledView scratch, RowScaledView quantized_output) {
+    auto &gpu = execution_context(output, {bias, e.residual, e.gate, e.condition, e.raw, e.residual_f32,
+                                           scratch.values, scratch.scales, quantized_output.values,
+                                           quantized_output.scales});
+    const auto *matrix = std::get_if<RowScaledView>(&weight);
+    if (!matrix) throw std::invalid_argument("this library only executes quantized weights");
+    if (!gpu.quantization) throw std::logic_error("context was created without a quantization mode");
+    if (e.bias.data) throw std::invalid_argument("linear already owns its bias");
+    for (const TensorView &source : {bias, e.residual, e.gate, e.condition})
+        if (source.overlaps(output))
+            throw std::invalid_argument("linear epilogue source aliases its projection output");
+    e.bias = bias;
+    matrix->validate();
+    RowScaledView activation;
+    if (const auto *dense = std::get_if<TensorView>(&input)) {
+        quantize_rows(*dense, scratch);
+        activation = scratch;
+    } else {
+        activation = std::get<RowScaledView>(input);
+    }
+    if (activation.values.cols != matrix->values.cols || output.rows != activation.values.rows ||
+        output.cols != matrix->values.rows || !output.dense())
+        throw std::invalid_argument("quantized linear dimensions/layout mismatch");
+    const bool plain = !e.bias.data && !e.residual.data && !e.residual_f32.data && !e.gate.data &&
+                       !e.condition.data && !e.raw.data && e.activation == Activation::Identity &&
+                       e.value_scale == 1 && e.output_scale == 1 && !e.valid_rows_per_sequence;
+    if (plain) gpu.quantization->linear(activation, *matrix, output);
+    else if (!gpu.quantization->linear_finish(activation, *matrix, output, e))
+        throw std::invalid_argument("epilogue cannot be fused into the quantized GEMM in this build");
+    if (quantized_output.values.data) quantize_rows(output, quantized_output);
+}
+} // namespace tts::ops

@@ -1,0 +1,130 @@
+#include "ops/quantized_gemm.h"
+#include "kernels/quant_dispatch.h"
+#include "ops/epilogue.h"
+#include <map>
+#include <tuple>
+
+namespace tts {
+namespace {
+using PlanKey = std::tuple<int, int, int, Type, int, int>;
+struct Plan {
+    LinearPath path;
+    int rows, channels, reduction;
+    Type output_type;
+    QuantizationGroups groups;
+};
+// reference: src/ops/cuda/quantization.cpp:94-102
+void check_linear(Type format, const RowScaledView &input, const RowScaledView &weight, const TensorView &output,
+                  int device) {
+    input.validate();
+    weight.validate();
+    if (input.values.type != format || weight.values.type != format ||
+        input.rotation_size != weight.rotation_size || input.values.cols != weight.values.cols ||
+        input.values.rows != output.rows || weight.values.rows != output.cols ||
+        (output.type != Type::BF16 && output.type != Type::F16) || !output.dense())
+        throw std::invalid_argument("quantized linear dimensions/type mismatch");
+    for (const TensorView *v : {&input.values, &input.scales, &weight.values, &weight.scales, &output})
+        if (v->device != device) throw std::invalid_argument("quantized linear operand is on another device");
+}
+} // namespace
+
+struct QuantizedGemm::Impl {
+    cudaStream_t stream;
+    Type format;
+    Buffer &workspace;
+    int multiprocessors = 0;
+    bool sealed = false;
+    std::map<PlanKey, Plan> plans;
+    SelectionStats stats;
+
+    const Plan *find(int rows, int channels, int reduction, Type type, int input_group, int weight_group) const {
+        auto it = plans.find(PlanKey{row_capacity(rows), channels, reduction, type, input_group, weight_group});
+        return it == plans.end() ? nullptr : &it->second;
+    }
+    void run(const Plan &plan, const RowScaledView &input, const RowScaledView &weight, const TensorView &output,
+             const ops::Epilogue *finish) {
+        launch_quant_linear(plan.path,
+                            {output.rows, plan.channels, plan.reduction, plan.groups.activation, plan.groups.weight},
+                            input.values.data, input.scales.ptr<float>(), weight.values.data,
+                            weight.scales.ptr<float>(), output.data, workspace.data(), workspace.size(), stream,
+                            format, plan.output_type, finish);
+    }
+};
+
+QuantizedGemm::QuantizedGemm(cudaStream_t stream, void *, Buffer &workspace, Type format)
+    : impl(new Impl{stream, format, workspace}) {
+    if (format != Type::FP8 && format != Type::I8) throw std::invalid_argument("unsupported quantized storage type");
+    quant_linear_initialize(workspace.device());
+    cudaDeviceProp p{};
+    if (cudaGetDeviceProperties(&p, workspace.device()) != cudaSuccess)
+        throw std::runtime_error("cudaGetDeviceProperties failed");
+    impl->multiprocessors = p.multiProcessorCount;
+    quant_linear_reset_workspace(workspace.data(), workspace.size(), stream);
+}
+QuantizedGemm::~QuantizedGemm() = default;
+void QuantizedGemm::seal() { impl->sealed = true; }
+QuantCacheStats QuantizedGemm::cache_stats() const {
+    QuantCacheStats s;
+    s.selection = impl->stats;
+    s.selection.entries = impl->plans.size();
+    s.prepared_plans = impl->plans.size();
+    return s;
+}
+void QuantizedGemm::prepare(int rows, int channels, int reduction, Type output_type, QuantizationGroups groups) {
+    if (output_type != Type::BF16 && output_type != Type::F16)
+        throw std::invalid_argument("quantized GEMM output must be F16 or BF16");
+    if (rows < 1 || channels < 1 || reduction < 1 || reduction % 16 || channels % 16)
+        throw std::invalid_argument("quantized GEMM unsupported shape");
+    if (impl->format == Type::I8 && reduction > INT32_MAX / (128 * 128))
+        throw std::invalid_argument("INT8 reduction can overflow INT32");
+    rows = row_capacity(rows);
+    PlanKey key{rows, channels, reduction, output_type, groups.activation, groups.weight};
+    if (impl->plans.count(key)) {
+        ++impl->stats.hits;
+        return;
+    }
+    if (impl->sealed) throw std::logic_error("prepared resource missing after initialization");
+    KernelProblem problem{rows, channels, reduction, groups.activation, groups.weight};
+    Plan plan{select_tcgen05_path(problem, impl->format, impl->multiprocessors, impl->workspace.size()), rows,
+              channels, reduction, output_type, groups};
+    if (quant_linear_workspace_bytes(plan.path, problem) > impl->workspace.size())
+        throw std::invalid_argument("quantized GEMM workspace too small for this shape");
+    ++impl->stats.searches;
+    impl->plans.emplace(key, plan);
+}
+void QuantizedGemm::prepare_finish(int rows, int channels, int reduction, Type output_type,
+                                   const ops::Epilogue &finish, QuantizationGroups groups) {
+    if (!ops::fusable(finish)) return;
+    if (!impl->find(rows, channels, reduction, output_type, groups.activation, groups.weight))
+        throw std::logic_error("quantized finish requires a prepared projection");
+}
+void QuantizedGemm::linear(RowScaledView input, RowScaledView weight, TensorView output) {
+    check_linear(impl->format, input, weight, output, impl->workspace.device());
+    const Plan *plan = impl->find(output.rows, output.cols, input.values.cols, output.type, input.group_size,
+                                  weight.group_size);
+    if (!plan) throw std::logic_error("quantized GEMM shape was not prepared before execution");
+    impl->run(*plan, input, weight, output, nullptr);
+}
+bool QuantizedGemm::linear_finish(RowScaledView input, RowScaledView weight, TensorView output,
+                                  const ops::Epilogue &finish) {
+    if (!ops::fusable(finish)) return false;
+    check_linear(impl->format, input, weight, output, impl->workspace.device());
+    const Plan *plan = impl->find(output.rows, output.cols, input.values.cols, output.type, input.group_size,
+                                  weight.group_size);
+    if (!plan) return false;
+    impl->run(*plan, input, weight, output, &finish);
+    return true;
+}
+bool QuantizedGemm::normalized_linear(TensorView, TensorView, TensorView, TensorView, float, const ops::NormFusion &,
+                                      RowScaledView, TensorView, const ops::Epilogue &, RowScaledView,
+                                      const QkvProjectionOutput *) {
+    return false;
+}
+LinearPath QuantizedGemm::planned_path(int rows, int channels, int reduction, Type output_type,
+                                       QuantizationGroups groups) const {
+    const Plan *plan = impl->find(rows, channels, reduction, output_type, groups.activation, groups.weight);
+    if (!plan) throw std::logic_error("quantized GEMM shape was not prepared before execution");
+    return plan->path;
+}
+int QuantizedGemm::status() const { return quant_linear_status(impl->workspace.data(), impl->stream); }
+} // namespace tts

@@ -1,0 +1,129 @@
+/* b200q — C ABI of the B200-native quantized linear path of breeze_tts_cpp.
+ *
+ * The reference engine exposes quantization only as the `quantization` string of tts_create
+ * (include/tts/tts.h:68-73); its quantized ops are internal C++ free functions. This header is the
+ * op-granular doorway a maintainer (or a test, or a non-C++ caller) binds instead of those
+ * internal functions. Every entry point cites the reference interface it stands in for.
+ *
+ * Conventions (same as the reference's bindings/c_api.cpp:25-40): every call returns 0 on success
+ * and -1 on failure, copying a message into `error` (capacity `error_capacity`, may be NULL).
+ * All device pointers are borrowed; nothing here allocates at call time except the *_create calls.
+ * Type codes are the integer values of the reference's tts::Type (src/core/tensor.h:8):
+ * BF16=0 F32=1 I32=2 FP8=3 I8=4 F16=5.
+ */
+#ifndef B200Q_H
+#define B200Q_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { B200Q_BF16 = 0, B200Q_F32 = 1, B200Q_I32 = 2, B200Q_FP8 = 3, B200Q_I8 = 4, B200Q_F16 = 5 };
+
+/* reference: tts::TensorView (src/core/tensor.h:27-119). stride in elements, 0 = dense. */
+typedef struct b200q_tensor {
+    void *data;
+    int32_t rows, cols, stride, type, device;
+} b200q_tensor;
+
+/* reference: tts::RowScaledView (src/core/quantization.h:33-49). scales are [rows] fp32, or
+ * group-major [ceil(cols/group_size), rows] when group_size != 0. */
+typedef struct b200q_row_scaled {
+    b200q_tensor values, scales;
+    int32_t group_size, rotation_size;
+} b200q_row_scaled;
+
+/* reference: tts::ops::Epilogue (src/ops/sequence.h:8-27), the fusable subset, plus the fp32
+ * residual of the synthetic decode workload. activation uses ops::Activation codes
+ * (src/ops/activation.h:4): 0 identity, 1 relu, 2 leaky relu, 3 silu, 4 gelu, 5 gelu-tanh, 7 tanh, 8 sigmoid. */
+typedef struct b200q_epilogue {
+    b200q_tensor bias, residual, residual_f32;
+    float value_scale, output_scale, residual_scale, alpha;
+    int32_t activation;
+} b200q_epilogue;
+
+/* reference: tts::LinearPath (src/ops/kernels/quant/kernel_config.h:5-9). kind 5 = tcgen05. */
+typedef struct b200q_path {
+    int32_t kind, tokens, channels, splits;
+} b200q_path;
+
+typedef struct b200q_context b200q_context;
+
+/* "b200q <version>; quantization=int8,fp8,group_int8,group_fp8" — reference: tts_version(). */
+const char *b200q_version(void);
+
+/* reference: CudaContext + QuantizedGemm construction (src/runtime/cuda_context.cpp:45-80).
+ * `quantization` is one of the reference's mode strings. `stream` is a cudaStream_t (NULL = default
+ * stream). `workspace` NULL lets the context own 8 MiB; otherwise it borrows the caller's memory,
+ * whose first 32 KiB it zeroes once. One-time device set-up happens here, so create the context
+ * before any stream capture. */
+int b200q_context_create(int32_t device, void *stream, void *workspace, size_t workspace_bytes,
+                         const char *quantization, b200q_context **out, char *error, size_t error_capacity);
+void b200q_context_destroy(b200q_context *);
+
+/* reference: ops::quantize_rows / launch_row_quantize (src/ops/storage.h:12,
+ * src/ops/kernels/quant/row_quantize.h:6). source is BF16 or F16. */
+int b200q_row_quantize(b200q_context *, const b200q_tensor *source, const b200q_row_scaled *destination,
+                       char *error, size_t error_capacity);
+
+/* reference: ops::quantized_norm / launch_quantized_norm (src/ops/basic.h:33-34,
+ * src/ops/kernels/quant/quant_norm.h:5-7). update, update_scale may have data == NULL. */
+int b200q_quantized_norm(b200q_context *, const b200q_tensor *residual, const b200q_tensor *update,
+                         const b200q_tensor *weight, const b200q_row_scaled *output, float epsilon,
+                         int32_t gemma, const b200q_tensor *update_scale, char *error, size_t error_capacity);
+
+/* reference: ops::quantized_gated / launch_quantized_gated (src/ops/basic.h:35,
+ * src/ops/kernels/quant/quant_gated.h:7-8). input is [rows, 2*K]; kind 0 SiLU, 1 tanh-GELU. */
+int b200q_quantized_gated(b200q_context *, const b200q_tensor *input, const b200q_row_scaled *output,
+                          int32_t kind, char *error, size_t error_capacity);
+
+/* reference: ops::prepare_quantized / QuantizedGemm::prepare (src/ops/basic.h:25-26,
+ * src/ops/cuda/quantization.h:27-28). Plans are keyed by the row-capacity class of `rows`. */
+int b200q_prepare(b200q_context *, int32_t rows, int32_t output_channels, int32_t input_channels,
+                  int32_t output_type, int32_t activation_group, int32_t weight_group, b200q_path *chosen,
+                  char *error, size_t error_capacity);
+/* reference: QuantizedGemm::seal / ops::seal (src/ops/cuda/quantization.h:24). */
+int b200q_seal(b200q_context *, char *error, size_t error_capacity);
+
+/* reference: ops::matmul(RowScaledView, RowScaledView, TensorView) / QuantizedGemm::linear and
+ * linear_finish (src/ops/basic.h:11, src/ops/cuda/quantization.h:31-33). epilogue may be NULL. */
+int b200q_linear(b200q_context *, const b200q_row_scaled *input, const b200q_row_scaled *weight,
+                 const b200q_tensor *output, const b200q_epilogue *epilogue, char *error, size_t error_capacity);
+
+/* reference: launch_quant_linear (src/ops/kernels/quant/quant_dispatch.h:11-15) with an explicit
+ * path, bypassing the plan cache. output type I32 returns the raw INT32 accumulators
+ * (per-row INT8 only, no epilogue). */
+int b200q_quant_linear(b200q_context *, const b200q_path *path, const b200q_row_scaled *input,
+                       const b200q_row_scaled *weight, const b200q_tensor *output, const b200q_epilogue *epilogue,
+                       char *error, size_t error_capacity);
+/* The path the planner would choose for a problem (reference: select_linear,
+ * src/ops/cuda/quantization_policy.h:32-33). */
+int b200q_select_path(b200q_context *, int32_t rows, int32_t output_channels, int32_t input_channels,
+                      int32_t activation_group, int32_t weight_group, b200q_path *chosen, char *error,
+                      size_t error_capacity);
+
+/* reference: ops::linear with a dense activation (src/ops/linear.h:11-14): quantize `input` into
+ * `scratch`, run the GEMM with bias/epilogue fused. */
+int b200q_linear_forward(b200q_context *, const b200q_tensor *input, const b200q_row_scaled *weight,
+                         const b200q_row_scaled *scratch, const b200q_tensor *output,
+                         const b200q_epilogue *epilogue, char *error, size_t error_capacity);
+
+/* Blocks until the context's stream is idle and returns the device status word through `status`:
+ * 0 = clean; nonzero = a bounded device-side wait gave up (results are invalid). */
+int b200q_status(b200q_context *, int32_t *status, char *error, size_t error_capacity);
+int b200q_multiprocessors(b200q_context *);
+
+/* Host-only helpers (no GPU needed). Row-capacity class of a token count — reference:
+ * row_capacity (src/core/row_capacity.h:10-19); returns -1 for invalid input. */
+int32_t b200q_row_capacity(int32_t rows, uint32_t bins_per_octave);
+/* The planner's choice without a context: pure function of the problem, the SM count and the
+ * workspace size. format is B200Q_I8 or B200Q_FP8. */
+int b200q_plan_path(int32_t rows, int32_t output_channels, int32_t input_channels, int32_t activation_group,
+                    int32_t weight_group, int32_t format, int32_t multiprocessors, size_t workspace_bytes,
+                    b200q_path *chosen, size_t *workspace_needed, char *error, size_t error_capacity);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,152 @@
+"""ctypes/numpy access to the CPU oracle (oracle/liboracle.so) and, where built, to the reference's
+own CUDA kernels (oracle/_ref/libttsref.so). Test infrastructure only."""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent.parent
+ORACLE_SO = ROOT / "oracle" / "liboracle.so"
+REF_SO = ROOT / "oracle" / "_ref" / "libttsref.so"
+BF16, F32, I32, FP8, I8, F16 = 0, 1, 2, 3, 4, 5
+
+
+class OracleEpilogue(C.Structure):
+    _fields_ = [("bias", C.c_void_p), ("residual", C.c_void_p), ("residual_f32", C.c_void_p),
+                ("value_scale", C.c_float), ("residual_scale", C.c_float), ("output_scale", C.c_float),
+                ("activation", C.c_int)]
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+class Oracle:
+    def __init__(self, lib):
+        self.lib = lib
+        lib.oracle_f32_to_bf16.restype = C.c_uint16
+        lib.oracle_f32_to_bf16.argtypes = [C.c_float]
+        lib.oracle_bf16_to_f32.restype = C.c_float
+        lib.oracle_bf16_to_f32.argtypes = [C.c_uint16]
+        lib.oracle_f16_to_f32.restype = C.c_float
+        lib.oracle_f16_to_f32.argtypes = [C.c_uint16]
+        for name in ("oracle_fp8_e4m3_encode", "oracle_fp8_e4m3_encode_toolkit", "oracle_int8_encode"):
+            getattr(lib, name).restype = C.c_uint8
+            getattr(lib, name).argtypes = [C.c_float]
+        lib.oracle_fp8_e4m3_decode.restype = C.c_float
+        lib.oracle_fp8_e4m3_decode.argtypes = [C.c_uint8]
+        lib.oracle_scale.restype = C.c_float
+        lib.oracle_scale.argtypes = [C.c_float, C.c_int]
+        lib.oracle_rotation_sign.restype = C.c_float
+        lib.oracle_rotation_sign.argtypes = [C.c_uint32]
+        lib.oracle_rotate128.argtypes = [C.c_void_p, C.c_int]
+        lib.oracle_row_quantize.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                            C.c_int, C.c_int, C.c_int]
+        lib.oracle_int8_accumulate.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        lib.oracle_quant_linear.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                            C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                            C.POINTER(OracleEpilogue), C.c_int]
+        lib.oracle_quantized_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                              C.c_float, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                              C.c_int]
+        lib.oracle_quantized_gated.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                               C.c_void_p, C.c_int, C.c_int, C.c_int]
+        lib.oracle_time_linear.restype = C.c_double
+        lib.oracle_time_linear.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                           C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int]
+        lib.oracle_hardware_threads.restype = C.c_int
+
+    # ---- helpers over numpy -------------------------------------------------------------------
+    def to_bf16(self, x: np.ndarray) -> np.ndarray:
+        """fp32 array -> bf16 bit patterns (uint16), round to nearest even."""
+        u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+        rounded = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+        return rounded.astype(np.uint16)
+
+    @staticmethod
+    def from_bf16(b: np.ndarray) -> np.ndarray:
+        return (b.astype(np.uint32) << 16).view(np.float32)
+
+    def row_quantize(self, src16: np.ndarray, fmt: int, group=0, rotation=0, src_type=BF16, stride=0):
+        rows, cols = src16.shape if stride == 0 else (src16.shape[0], src16.shape[1])
+        src16 = np.ascontiguousarray(src16)
+        values = np.zeros((rows, cols), dtype=np.uint8)
+        scales = np.zeros(((cols + group - 1) // group, rows) if group else (rows,), dtype=np.float32)
+        self.lib.oracle_row_quantize(_ptr(src16), src_type, rows, cols, stride, _ptr(values), _ptr(scales), fmt, group,
+                                     rotation)
+        return values, scales
+
+    def int8_accumulate(self, xq: np.ndarray, wq: np.ndarray) -> np.ndarray:
+        m, k = xq.shape
+        n = wq.shape[0]
+        acc = np.zeros((m, n), dtype=np.int32)
+        self.lib.oracle_int8_accumulate(_ptr(np.ascontiguousarray(xq)), _ptr(np.ascontiguousarray(wq)), m, n, k, _ptr(acc))
+        return acc
+
+    def quant_linear(self, xq, sx, wq, sw, fmt, group_x=0, group_w=0, out_type=BF16, bias=None, residual=None,
+                     residual_f32=None, activation=0, value_scale=1.0, residual_scale=1.0, output_scale=1.0, threads=8):
+        m, k = xq.shape
+        n = wq.shape[0]
+        out = np.zeros((m, n), dtype=np.uint16)
+        exact = np.zeros((m, n), dtype=np.float32)
+        keep = [np.ascontiguousarray(a) if a is not None else None for a in (bias, residual, residual_f32)]
+        ep = OracleEpilogue(_ptr(keep[0]), _ptr(keep[1]), _ptr(keep[2]), value_scale, residual_scale, output_scale,
+                            activation)
+        self.lib.oracle_quant_linear(_ptr(np.ascontiguousarray(xq)), _ptr(np.ascontiguousarray(sx)),
+                                     _ptr(np.ascontiguousarray(wq)), _ptr(np.ascontiguousarray(sw)), m, n, k, group_x,
+                                     group_w, fmt, out_type, _ptr(out), _ptr(exact), C.byref(ep), threads)
+        return out, exact
+
+    def quantized_norm(self, residual16, update16, weight16, fmt, eps, gemma=False, update_scale16=None, group=0,
+                       rotation=0, type_=BF16):
+        rows, cols = residual16.shape
+        residual16 = np.ascontiguousarray(residual16).copy()
+        normalized = np.zeros((rows, cols), dtype=np.uint16)
+        values = np.zeros((rows, cols), dtype=np.uint8)
+        scales = np.zeros(((cols + group - 1) // group, rows) if group else (rows,), dtype=np.float32)
+        upd = np.ascontiguousarray(update16) if update16 is not None else None
+        us = np.ascontiguousarray(update_scale16) if update_scale16 is not None else None
+        self.lib.oracle_quantized_norm(_ptr(residual16), _ptr(upd), _ptr(np.ascontiguousarray(weight16)), _ptr(us), rows,
+                                       cols, type_, eps, int(gemma), _ptr(normalized), _ptr(values), _ptr(scales), fmt,
+                                       group, rotation)
+        return residual16, normalized, values, scales
+
+    def quantized_gated(self, input16, fmt, kind=0, group=0, rotation=0, type_=BF16):
+        rows, two = input16.shape
+        width = two // 2
+        activated = np.zeros((rows, width), dtype=np.uint16)
+        values = np.zeros((rows, width), dtype=np.uint8)
+        scales = np.zeros(((width + group - 1) // group, rows) if group else (rows,), dtype=np.float32)
+        self.lib.oracle_quantized_gated(_ptr(np.ascontiguousarray(input16)), rows, width, type_, kind, _ptr(activated),
+                                        _ptr(values), _ptr(scales), fmt, group, rotation)
+        return activated, values, scales
+
+
+def build_oracle():
+    subprocess.run(["make", "-C", str(ROOT / "oracle"), "oracle"], check=True, capture_output=True)
+
+
+def load() -> Oracle:
+    if not ORACLE_SO.exists():
+        build_oracle()
+    return Oracle(C.CDLL(str(ORACLE_SO)))
+
+
+def load_reference():
+    if not REF_SO.exists():
+        return None
+    lib = C.CDLL(str(REF_SO))
+    lib.ttsref_last_error.restype = C.c_char_p
+    lib.ttsref_row_quantize.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
+                                        C.c_int, C.c_int, C.c_void_p]
+    lib.ttsref_quant_linear.argtypes = [C.c_int] * 9 + [C.c_void_p] * 6 + [C.c_size_t, C.c_void_p, C.c_int, C.c_int]
+    lib.ttsref_quantized_norm.argtypes = [C.c_void_p] * 4 + [C.c_int] * 3 + [C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                                                             C.c_int, C.c_float, C.c_int, C.c_void_p]
+    lib.ttsref_quantized_gated.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p] + [C.c_int] * 6 + [C.c_void_p]
+    lib.ttsref_residual_add_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.ttsref_candidates.argtypes = [C.c_int] * 6 + [C.c_size_t, C.c_size_t, C.c_void_p, C.c_int]
+    lib.ttsref_select.argtypes = [C.c_int] * 7 + [C.c_size_t, C.c_void_p, C.c_char_p, C.c_int]
+    return lib
