@@ -1,0 +1,207 @@
+"""Pins of the CPU oracle. The reference ships no tests or golden vectors for this path, so the
+pins are hand-derived known answers for every rule the oracle restates (each test names the
+reference lines the rule comes from), algebraic properties, and the committed fixtures in
+tests/golden/."""
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from tests import synth
+from tests.oracle_binding import BF16, F16, FP8, I8
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def test_int8_round_half_even_and_clamp(oracle):
+    # reference: src/ops/kernels/quant/quant_format.cuh:37-47 — clamp to +-127, then ties to even; -128 never appears
+    cases = {0.5: 0, 1.5: 2, 2.5: 2, -0.5: 0, -1.5: -2, -2.5: -2, 126.5: 126, 127.5: 127, -127.5: -127,
+             1e9: 127, -1e9: -127, 0.49999997: 0, 126.50001: 127}
+    for value, want in cases.items():
+        assert np.int8(np.uint8(oracle.lib.oracle_int8_encode(value))) == want, value
+
+
+def test_scale_rule(oracle):
+    # reference: quant_format.cuh:62-64
+    assert oracle.lib.oracle_scale(0.0, I8) == 1.0
+    assert oracle.lib.oracle_scale(127.0, I8) == 1.0
+    assert oracle.lib.oracle_scale(448.0, FP8) == 1.0
+    assert oracle.lib.oracle_scale(1.0, I8) == np.float32(1.0) / np.float32(127.0)
+    tiny = np.float32(1e-45)
+    assert oracle.lib.oracle_scale(float(tiny), I8) == np.finfo(np.float32).tiny  # floor at FLT_MIN
+
+
+def test_fp8_known_answers(oracle):
+    # reference: quant_format.cuh:12-22 (cuda_fp8.h conversions): RN-even, saturate to 448, subnormals down to 2^-9
+    enc, dec = oracle.lib.oracle_fp8_e4m3_encode, oracle.lib.oracle_fp8_e4m3_decode
+    assert dec(enc(1.0625)) == 1.0 and dec(enc(1.1875)) == 1.25  # ties to even
+    assert dec(enc(460.0)) == 448.0 and dec(enc(1e9)) == 448.0 and dec(enc(-1e9)) == -448.0
+    assert enc(2.0 ** -10) == 0 and enc(2.0 ** -9) == 1 and enc(3 * 2.0 ** -10) == 2
+    assert enc(0.0) == 0 and enc(-0.0) == 0x80
+    assert dec(0x7E) == 448.0 and dec(0x08) == 2.0 ** -6 and dec(0x01) == 2.0 ** -9
+
+
+def test_fp8_software_encoder_equals_toolkit_conversion(oracle):
+    rng = np.random.default_rng(0)
+    values = np.concatenate([rng.standard_normal(20000) * s for s in (1e-3, 0.05, 1, 30, 500)]).astype(np.float32)
+    exact = np.array([oracle.lib.oracle_fp8_e4m3_decode(q) for q in range(256) if q & 0x7F != 0x7F], dtype=np.float32)
+    mids = ((exact[:-1].astype(np.float64) + exact[1:]) / 2).astype(np.float32)  # exact ties between neighbours
+    for v in np.concatenate([values, exact, mids, np.nextafter(mids, 1e9), np.nextafter(mids, -1e9)]):
+        assert oracle.lib.oracle_fp8_e4m3_encode(float(v)) == oracle.lib.oracle_fp8_e4m3_encode_toolkit(float(v)), v
+
+
+def test_fp8_decode_encode_round_trip(oracle):
+    for q in range(256):
+        if q & 0x7F == 0x7F:
+            continue
+        assert oracle.lib.oracle_fp8_e4m3_encode(oracle.lib.oracle_fp8_e4m3_decode(q)) == q
+
+
+def test_bf16_and_f16_conversions(oracle):
+    assert oracle.lib.oracle_f32_to_bf16(1.0) == 0x3F80
+    assert oracle.lib.oracle_f32_to_bf16(float(np.float32(1.00390625))) == 0x3F80  # tie -> even
+    assert oracle.lib.oracle_f32_to_bf16(float(np.float32(1.01171875))) == 0x3F82  # tie -> even (up)
+    rng = np.random.default_rng(1)
+    x = (rng.standard_normal(4096) * 3).astype(np.float32)
+    assert np.array_equal(oracle.to_bf16(x), np.array([oracle.lib.oracle_f32_to_bf16(float(v)) for v in x], dtype=np.uint16))
+    halves = rng.integers(0, 0x7C00, 4096, dtype=np.uint16)
+    want = halves.view(np.float16).astype(np.float32)
+    got = np.array([oracle.lib.oracle_f16_to_f32(int(h)) for h in halves], dtype=np.float32)
+    assert np.array_equal(got, want)
+
+
+def test_rotation_sign_hash(oracle):
+    # reference: src/ops/kernels/quant/quant_device.cuh:100-104 — 32-bit wraparound integer hash of the column
+    def sign(j):
+        h = (j * 0x45D9F3B) & 0xFFFFFFFF
+        h = ((h ^ (h >> 16)) * 0x45D9F3B) & 0xFFFFFFFF
+        return 1.0 if (h ^ (h >> 16)) & 1 else -1.0
+    for j in list(range(300)) + [6143, 65535, 2 ** 31 - 1]:
+        assert oracle.lib.oracle_rotation_sign(j) == sign(j)
+
+
+def _rotate(oracle, v, column=0):
+    buf = np.ascontiguousarray(v, dtype=np.float32).copy()
+    oracle.lib.oracle_rotate128(buf.ctypes.data, column)
+    return buf
+
+
+def test_rotation_is_signed_sylvester_hadamard(oracle):
+    # reference: quant_device.cuh:96-125. The butterfly network equals H128 (Sylvester order) / sqrt(128) applied to D x.
+    h = np.array([[1.0]])
+    while h.shape[0] < 128:
+        h = np.block([[h, h], [h, -h]])
+    rng = np.random.default_rng(2)
+    x = rng.integers(-8, 9, 128).astype(np.float32)  # small integers: every butterfly sum is exact
+    signs = np.array([oracle.lib.oracle_rotation_sign(256 + j) for j in range(128)], dtype=np.float32)
+    want = ((h @ (x * signs).astype(np.float64)) * 0.08838834764831845).astype(np.float32)
+    assert np.array_equal(_rotate(oracle, x, 256), (h @ (x * signs)).astype(np.float32) * np.float32(0.08838834764831845))
+    assert np.allclose(_rotate(oracle, x, 256), want, rtol=1e-6)
+
+
+def test_rotation_preserves_norm_and_dot_product(oracle):
+    rng = np.random.default_rng(3)
+    x, w = rng.standard_normal(128).astype(np.float32), rng.standard_normal(128).astype(np.float32)
+    rx, rw = _rotate(oracle, x, 384), _rotate(oracle, w, 384)
+    assert abs(np.linalg.norm(rx) - np.linalg.norm(x)) < 1e-4 * np.linalg.norm(x)
+    assert abs(float(rx @ rw) - float(x @ w)) < 1e-4 * np.linalg.norm(x) * np.linalg.norm(w)
+
+
+def test_unsigned_transform_twice_is_identity(oracle):
+    # With all signs equal the matrix is symmetric orthogonal: applying it twice returns the input.
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal(128).astype(np.float32)
+    signs = np.array([oracle.lib.oracle_rotation_sign(j) for j in range(128)], dtype=np.float32)
+    once = _rotate(oracle, x * signs, 0)          # D cancels: H/sqrt(128) x
+    twice = _rotate(oracle, once * signs, 0)
+    assert np.allclose(twice, x, atol=1e-5)
+
+
+def test_row_quantize_layouts(oracle):
+    x = synth.activations(5, 384, seed=9)
+    x16 = oracle.to_bf16(x)
+    xf = oracle.from_bf16(x16)
+    q, s = oracle.row_quantize(x16, I8)
+    assert s.shape == (5,) and np.array_equal(s, np.abs(xf).max(axis=1) / np.float32(127))
+    assert np.abs(q.view(np.int8).astype(np.int32)).max() == 127
+    qg, sg = oracle.row_quantize(x16, I8, group=128)
+    assert sg.shape == (3, 5)  # group-major: [K/128, rows]
+    for g in range(3):
+        assert np.array_equal(sg[g], np.abs(xf[:, g * 128:(g + 1) * 128]).max(axis=1) / np.float32(127))
+    # ragged tail group (reference: quant_device.cuh:63-88 handles columns - column remaining)
+    q2, s2 = oracle.row_quantize(np.ascontiguousarray(x16[:, :200]), I8, group=128)
+    assert s2.shape == (2, 5) and np.array_equal(s2[1], np.abs(xf[:, 128:200]).max(axis=1) / np.float32(127))
+    zeros = np.zeros((2, 128), dtype=np.uint16)
+    qz, sz = oracle.row_quantize(zeros, FP8, group=128, rotation=128)
+    assert not (qz & 0x7F).any() and np.all(sz == 1.0)  # -0.0 keeps its sign bit, as on the GPU
+
+
+def test_dequantized_linear_tracks_float_matmul(oracle):
+    m, n, k = 8, 96, 512
+    x16, w16 = oracle.to_bf16(synth.activations(m, k, 1, outlier_columns=0)), oracle.to_bf16(synth.weights(n, k, 2))
+    truth = oracle.from_bf16(x16).astype(np.float64) @ oracle.from_bf16(w16).astype(np.float64).T
+    for fmt, group, rotation, tol in ((I8, 0, 0, 0.03), (FP8, 0, 0, 0.08), (I8, 128, 128, 0.03), (FP8, 128, 128, 0.08)):
+        xq, sx = oracle.row_quantize(x16, fmt, group, rotation)
+        wq, sw = oracle.row_quantize(w16, fmt, group, rotation)
+        _, exact = oracle.quant_linear(xq, sx, wq, sw, fmt, group, group, threads=2)
+        assert np.abs(exact - truth).max() < tol * np.abs(truth).max(), (fmt, group)
+
+
+def test_int8_accumulators_are_exact_integers(oracle):
+    rng = np.random.default_rng(5)
+    xq = rng.integers(-127, 128, (4, 256), dtype=np.int8)
+    wq = rng.integers(-127, 128, (32, 256), dtype=np.int8)
+    want = xq.astype(np.int64) @ wq.astype(np.int64).T
+    assert np.array_equal(oracle.int8_accumulate(xq, wq), want.astype(np.int32))
+    ones = np.full((1, 6144), 127, dtype=np.int8)
+    assert oracle.int8_accumulate(ones, ones)[0, 0] == 6144 * 127 * 127  # the largest sum the path can see
+
+
+def test_epilogue_rounding_chain(oracle):
+    # reference: src/ops/kernels/sequence/sequence_internal.cuh:52-74 — every step rounds to the storage type
+    xq = np.full((1, 16), 3, dtype=np.uint8)
+    wq = np.full((16, 16), 5, dtype=np.uint8)
+    sx, sw = np.array([0.5], dtype=np.float32), np.full(16, 0.25, dtype=np.float32)
+    base = 16 * 15 * 0.5 * 0.25  # 30
+    bias = oracle.to_bf16(np.full(16, 0.0078125, dtype=np.float32))  # 2^-7: lost when added to 30 in bf16
+    out, _ = oracle.quant_linear(xq, sx, wq, sw, I8, bias=bias)
+    assert np.all(oracle.from_bf16(out) == base)
+    res = np.full((1, 16), -100.0, dtype=np.float32)
+    out, _ = oracle.quant_linear(xq, sx, wq, sw, I8, residual_f32=res, activation=1)
+    assert np.all(oracle.from_bf16(out) == 0.0)  # relu(30 - 100)
+
+
+def test_golden_fixtures(oracle):
+    """Fixtures made by tests/golden/make_golden.py from this oracle on seeded inputs: they freeze the
+    oracle's answers so that a later change to it cannot drift unnoticed."""
+    index = json.loads((GOLDEN / "index.json").read_text())
+    assert index["cases"], "no golden cases"
+    for case in index["cases"]:
+        data = np.load(GOLDEN / case["file"])
+        fmt, group, rotation = case["format"], case["group"], case["rotation"]
+        q, s = oracle.row_quantize(data["x16"], fmt, group, rotation)
+        assert np.array_equal(q, data["xq"]) and np.array_equal(s.view(np.uint32), data["sx"].view(np.uint32)), case
+        wq, sw = oracle.row_quantize(data["w16"], fmt, group, rotation)
+        assert np.array_equal(wq, data["wq"]) and np.array_equal(sw.view(np.uint32), data["sw"].view(np.uint32)), case
+        out, _ = oracle.quant_linear(q, s, wq, sw, fmt, group, group, threads=2)
+        assert np.array_equal(out, data["out16"]), case
+        if fmt == I8 and not group:
+            assert np.array_equal(oracle.int8_accumulate(q.view(np.int8), wq.view(np.int8)), data["acc"]), case
+
+
+def test_producers_keep_reference_rounding_points(oracle):
+    # reference: quant_norm.cu:14-123 and quant_gated.cu:18-85
+    rng = np.random.default_rng(6)
+    x16 = oracle.to_bf16(rng.standard_normal((3, 256)).astype(np.float32))
+    w16 = oracle.to_bf16((1 + 0.1 * rng.standard_normal(256)).astype(np.float32))
+    _, normalized, q, s = oracle.quantized_norm(x16, None, w16, I8, 1e-6)
+    xf, wf = oracle.from_bf16(x16), oracle.from_bf16(w16)
+    approx = xf / np.sqrt((xf.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + 1e-6) * wf
+    assert np.abs(oracle.from_bf16(normalized) - approx).max() < 0.03
+    q2, s2 = oracle.row_quantize(normalized, I8)
+    assert np.array_equal(q, q2) and np.array_equal(s, s2)  # the tail is the plain row quantizer
+    gu16 = oracle.to_bf16(rng.standard_normal((2, 512)).astype(np.float32))
+    act, q, s = oracle.quantized_gated(gu16, I8, kind=0)
+    g, u = oracle.from_bf16(gu16[:, :256]), oracle.from_bf16(gu16[:, 256:])
+    assert np.abs(oracle.from_bf16(act) - g / (1 + np.exp(-g)) * u).max() < 0.03
