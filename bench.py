@@ -1,0 +1,550 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized linear hot path (see DESIGN.md for the definitions).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200q|reference|reference-cpu]
+
+Workload (`config.workload`): the quantized linears of a synthetic 28-layer decoder stack
+(hidden 2048, fused QKV 4096, O 2048, fused gate+up 12288, down 6144->2048; INT8 W8A8 with
+per-channel weight scales and dynamic per-token activation scales), 64 concurrent decode streams
+sharded data-parallel over the GPUs (64/N rows per GPU), weights replicated. One step = one decode
+step: for every layer quantize -> QKV GEMM, quantize -> O GEMM (+fp32 residual), quantize ->
+gate/up GEMM, SiLU-gate+quantize -> down GEMM (+fp32 residual); 224 kernel launches replayed as one
+CUDA graph. A step streams 1.41 GB of distinct weights, far more than the 126 MB L2.
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HIDDEN, QKV, FFN, LAYERS, STREAMS = 2048, 4096, 6144, 28, 64
+SHAPES = {"qkv": (HIDDEN, QKV), "o": (HIDDEN, HIDDEN), "gate_up": (HIDDEN, 2 * FFN), "down": (FFN, HIDDEN)}  # name: (K, N)
+SEED = 0x5EED
+
+
+# ------------------------------------------------------------------------------------------------
+# algorithmic bytes / ops (per linear, per-channel modes): quantize 2MK read + MK+4M written;
+# GEMM MK + NK + 4(M+N) read + 2MN written (+4MN when an fp32 residual is read); ops 2MNK.
+def linear_bytes(m, k, n, residual=False, group=0, quantize=True):
+    scales = 4 * (m + n) * (k // group if group else 1)
+    gemm = m * k + n * k + scales + 2 * m * n + (4 * m * n if residual else 0)
+    quant = (2 * m * k + m * k + 4 * m * (k // group if group else 1)) if quantize else 0
+    return gemm + quant
+
+
+def step_bytes(m, gemm_only=False):
+    total = 0
+    for name, (k, n) in SHAPES.items():
+        total += linear_bytes(m, k, n, residual=name in ("o", "down"), quantize=not gemm_only)
+    return total * LAYERS
+
+
+def step_ops(m):
+    return LAYERS * sum(2 * m * k * n for k, n in SHAPES.values())
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data.get("bf16_tflops", 0)), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc, self.index = None, gpu_index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.samples = []
+        if not self.proc:
+            return
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 9 and parts[1].replace(".", "").isdigit():
+                self.samples.append(parts)
+
+    def summary(self):
+        if not getattr(self, "samples", None):
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = [float(s[1]) for s in self.samples]
+        busy = [v for v in sm if v > 0.5 * max(sm)] or sm
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[5 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": float(self.samples[0][2]), "reasons": reasons,
+                "samples": len(sm), "power_w_max": max(float(s[3]) for s in self.samples if s[3].replace(".", "").isdigit())}
+
+
+# ------------------------------------------------------------------------------------------------
+def synth_activations(torch, rows, cols, seed, device, outlier_fraction=0.005):
+    g = torch.Generator(device=device).manual_seed(seed)
+    x = torch.randn(rows, cols, generator=g, device=device, dtype=torch.float32)
+    count = max(1, round(cols * outlier_fraction))
+    columns = torch.randperm(cols, generator=g, device=device)[:count]
+    x[:, columns] *= 20.0
+    return x
+
+
+def synth_weight(torch, n, k, seed, device):
+    g = torch.Generator(device=device).manual_seed(seed)
+    return (torch.randn(n, k, generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+
+
+class Stack:
+    """Weights (quantized once at load, like the reference's Weights::quantized) and activation buffers."""
+
+    def __init__(self, torch, ops, ctx, rows, device, fmt, layers=LAYERS):
+        self.rows, self.layers = rows, layers
+        self.weights = []
+        for layer in range(layers):
+            entry = {}
+            for i, (name, (k, n)) in enumerate(SHAPES.items()):
+                w = synth_weight(torch, n, k, SEED + 17 * layer + i, device)
+                view = ops.RowScaledView.empty(n, k, fmt, device=device)
+                ctx.quantize_rows(w, view)
+                entry[name] = view
+            self.weights.append(entry)
+        torch.cuda.synchronize(device)
+        self.x = synth_activations(torch, rows, HIDDEN, SEED - 1, device).to(torch.bfloat16)
+        self.residual = synth_activations(torch, rows, HIDDEN, SEED - 2, device, outlier_fraction=0.0)
+        self.h = torch.empty(rows, HIDDEN, dtype=torch.bfloat16, device=device)
+        self.qkv = torch.empty(rows, QKV, dtype=torch.bfloat16, device=device)
+        self.gu = torch.empty(rows, 2 * FFN, dtype=torch.bfloat16, device=device)
+        self.q_hidden = ops.RowScaledView.empty(rows, HIDDEN, fmt, device=device)
+        self.q_ffn = ops.RowScaledView.empty(rows, FFN, fmt, device=device)
+
+
+def run_b200q(args, torch, dist, rank, world, device):
+    from breeze_tts_cpp_b200 import I8, ops
+    rows = STREAMS // world
+    stream = torch.cuda.Stream(device=device)
+    with torch.cuda.stream(stream):
+        ctx = ops.Context("int8", device=device.index, stream=stream, workspace_bytes=8 << 20)
+        stack = Stack(torch, ops, ctx, rows, device, I8)
+        for k, n in SHAPES.values():
+            ctx.prepare_quantized(rows, n, k)
+        ctx.seal()
+
+        def decode_step(gemm_only=False):
+            h = stack.h
+            for layer in stack.weights:
+                if not gemm_only:
+                    ctx.quantize_rows(h, stack.q_hidden)
+                ctx.matmul(stack.q_hidden, layer["qkv"], stack.qkv)
+                if not gemm_only:
+                    ctx.quantize_rows(stack.qkv[:, :HIDDEN], stack.q_hidden)
+                ctx.matmul(stack.q_hidden, layer["o"], h, residual_f32=stack.residual)
+                if not gemm_only:
+                    ctx.quantize_rows(h, stack.q_hidden)
+                ctx.matmul(stack.q_hidden, layer["gate_up"], stack.gu)
+                if not gemm_only:
+                    ctx.quantized_gated(stack.gu, stack.q_ffn, 0)
+                ctx.matmul(stack.q_ffn, layer["down"], h, residual_f32=stack.residual)
+
+        stack.h.copy_(stack.x)
+        decode_step()  # eager once: plans, tensor maps, lazy module loading
+        stream.synchronize()
+        assert ctx.status() == 0, "device status word set"
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            decode_step()
+        gemm_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gemm_graph, stream=stream):
+            decode_step(gemm_only=True)
+
+    launches_per_step = LAYERS * 8
+    result = time_steps(args, torch, dist, world, device, stream, stack, graph, gemm_graph)
+    assert ctx.status() == 0, "device status word set during the timed region"
+    result["gpu_launches"] = launches_per_step * args.steps
+    extras = {}
+    if rank == 0 and world == 1 and not args.no_sweep:
+        extras = sweep(torch, ops, device, stream)
+    return result, extras
+
+
+def time_steps(args, torch, dist, world, device, stream, stack, graph, gemm_graph):
+    """value: K graph replays with inputs resident; e2e: per step H2D of the step input, replay, D2H of the
+    step result, stream sync; roofline: K replays of the GEMM launches alone."""
+    host_x = stack.x.cpu().pin_memory()
+    host_out = torch.empty(stack.rows, HIDDEN, dtype=torch.bfloat16).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    def timed(fn, steps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        with torch.cuda.stream(stream):
+            start.record(stream)
+            for _ in range(steps):
+                fn()
+            stop.record(stream)
+        stop.synchronize()
+        barrier()
+        ms = start.elapsed_time(stop)
+        if world > 1:
+            t = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def resident_step():
+        stack.h.copy_(stack.x, non_blocking=True)  # device-to-device reset of the step input
+        graph.replay()
+
+    def e2e_step():
+        stack.h.copy_(host_x, non_blocking=True)
+        graph.replay()
+        host_out.copy_(stack.h, non_blocking=True)
+        stream.synchronize()
+
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            resident_step()
+        stream.synchronize()
+    with ClockSampler(device.index) as clocks:
+        ms_value = timed(resident_step, args.steps)
+    with torch.cuda.stream(stream):
+        for _ in range(max(1, args.warmup // 2)):
+            e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+    with torch.cuda.stream(stream):
+        for _ in range(max(1, args.warmup // 2)):
+            gemm_graph.replay()
+    ms_gemm = timed(gemm_graph.replay, args.steps)
+    return {"ms_value": ms_value, "ms_e2e": ms_e2e, "ms_gemm": ms_gemm, "clocks": clocks.summary(),
+            "h2d": host_x.numel() * 2, "d2h": host_out.numel() * 2}
+
+
+def sweep(torch, ops, device, stream):
+    """Per-shape numbers for the other configurations (decode sweep, FP8 prefill, K-group down projection),
+    each rotated over enough distinct weight copies to exceed L2. Reported beside the headline, not as it."""
+    from breeze_tts_cpp_b200 import FP8, I8
+    peaks = measured_peaks()
+    rows_out = []
+
+    def measure(mode, fmt, m, k, n, group, residual, iters=20):
+        ctx = ops.Context(mode, device=device.index, stream=stream, workspace_bytes=8 << 20)
+        copies = max(2, min(24, (300 << 20) // (n * k)))
+        rot = 128 if group else 0
+        with torch.cuda.stream(stream):
+            ws = []
+            for c in range(copies):
+                w = synth_weight(torch, n, k, SEED + c, device)
+                ws.append(ctx.quantize_rows(w, ops.RowScaledView.empty(n, k, fmt, group, rot, device=device)))
+            x = synth_activations(torch, m, k, SEED, device).to(torch.bfloat16)
+            xq = ops.RowScaledView.empty(m, k, fmt, group, rot, device=device)
+            out = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+            res = torch.randn(m, n, device=device) if residual else None
+            path = ctx.prepare_quantized(m, n, k)
+            kw = {"residual_f32": res} if residual else {}
+
+            def body():
+                for w in ws:
+                    ctx.quantize_rows(x, xq)
+                    ctx.matmul(xq, w, out, **kw)
+            body()
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                body()
+            g.replay()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(1, iters // copies)
+            start.record(stream)
+            for _ in range(reps):
+                g.replay()
+            stop.record(stream)
+            stop.synchronize()
+        status = ctx.status()
+        ctx.close()
+        us = start.elapsed_time(stop) * 1e3 / (reps * copies)
+        nbytes = linear_bytes(m, k, n, residual, group)
+        tops = 2.0 * m * n * k / us / 1e6
+        return {"mode": mode, "m": m, "k": k, "n": n, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
+                "tops": round(tops, 1), "hbm_frac_measured": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 3),
+                "path": list(path), "status": status}
+
+    for m in (1, 4, 16, 64):
+        for name, (k, n) in SHAPES.items():
+            rows_out.append(dict(measure("int8", I8, m, k, n, 0, True), config="c2_decode", shape=name))
+    for m in (2048, 8192):
+        for name, (k, n) in SHAPES.items():
+            rows_out.append(dict(measure("fp8", FP8, m, k, n, 0, False, iters=6), config="c3_prefill_fp8", shape=name))
+    for mode, fmt in (("group_int8", I8), ("group_fp8", FP8)):
+        for m in (16, 4096):
+            rows_out.append(dict(measure(mode, fmt, m, FFN, HIDDEN, 128, False, iters=8), config="c4_group_down", shape="down"))
+    return {"sweep": rows_out}
+
+
+# ------------------------------------------------------------------------------------------------
+def cpu_baseline(rows, max_seconds=20.0):
+    """Scalar host-core port (the CPU oracle) on a bounded sample: one decoder layer's four linears."""
+    import numpy as np
+    from tests import oracle_binding
+    oracle = oracle_binding.load()
+    threads = oracle.lib.oracle_hardware_threads()
+    rng = np.random.default_rng(SEED)
+    total_bytes, total_s = 0, 0.0
+    done = []
+    for name, (k, n) in SHAPES.items():
+        x16 = oracle.to_bf16(rng.standard_normal((rows, k)).astype(np.float32))
+        wq = rng.integers(-127, 128, (n, k), dtype=np.int8).view(np.uint8)
+        sw = np.full(n, 1e-3, dtype=np.float32)
+        out = np.zeros((rows, n), dtype=np.uint16)
+        residual = rng.standard_normal((rows, n)).astype(np.float32) if name in ("o", "down") else None
+        seconds = oracle.lib.oracle_time_linear(x16.ctypes.data, wq.ctypes.data, sw.ctypes.data, rows, n, k, n, 4, 0, 0,
+                                                out.ctypes.data, residual.ctypes.data if residual is not None else None,
+                                                threads)
+        total_s += seconds
+        total_bytes += linear_bytes(rows, k, n, residual is not None)
+        done.append(name)
+        if total_s > max_seconds:
+            break
+    return {"value": round(total_bytes / total_s / 1e9, 4), "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"one decoder layer ({'+'.join(done)}) at M={rows}: quantize+GEMM+dequant in {total_s:.2f} s"}
+
+
+# ------------------------------------------------------------------------------------------------
+def run_reference(args, torch, dist, rank, world, device):
+    """The reference's own CUDA kernels (built from its sources into oracle/_ref/libttsref.so) on the same chain.
+    The reference has no CPU implementation of this path; its stock code path on sm_100 is the CUTLASS SM80
+    GEMM / scalar GEMV chosen per shape, here by timing every candidate its planner enumerates."""
+    from tests import oracle_binding
+    lib = oracle_binding.load_reference()
+    if lib is None:
+        return None
+    from breeze_tts_cpp_b200 import I8, ops
+    rows = STREAMS // world
+    BF16 = 0
+    stream = torch.cuda.Stream(device=device)
+    sp = C.c_void_p(stream.cuda_stream)
+    with torch.cuda.stream(stream):
+        ctx = ops.Context("int8", device=device.index, stream=stream)  # only to own buffers' helper types
+        stack = Stack(torch, ops, ctx, rows, device, I8)
+        # the reference quantizes its own weights too: overwrite with its kernel so nothing of ours is on the path
+        for layer_index, layer in enumerate(stack.weights):
+            for i, (name, (k, n)) in enumerate(SHAPES.items()):
+                w = synth_weight(torch, n, k, SEED + 17 * layer_index + i, device)
+                rc = lib.ttsref_row_quantize(w.data_ptr(), n, k, 0, BF16, layer[name].values.data_ptr(),
+                                             layer[name].scales.data_ptr(), I8, 0, 0, sp)
+                assert rc == 0, lib.ttsref_last_error()
+        ctx.close()
+        workspace = torch.zeros(8 << 20, dtype=torch.uint8, device=device)
+        props = torch.cuda.get_device_properties(device)
+
+        def gemm(path, xq, w, out, k, n):
+            rc = lib.ttsref_quant_linear(path[0], path[1], path[2], path[3], rows, n, k, 0, 0, xq.values.data_ptr(),
+                                         xq.scales.data_ptr(), w.values.data_ptr(), w.scales.data_ptr(), out.data_ptr(),
+                                         workspace.data_ptr(), workspace.numel(), sp, I8, BF16)
+            if rc != 0:
+                raise RuntimeError(lib.ttsref_last_error().decode())
+
+        def quantize(x, q):
+            stride = x.stride(0) if x.stride(0) != x.shape[1] else 0
+            rc = lib.ttsref_row_quantize(x.data_ptr(), x.shape[0], x.shape[1], stride, BF16, q.values.data_ptr(),
+                                         q.scales.data_ptr(), I8, 0, 0, sp)
+            assert rc == 0, lib.ttsref_last_error()
+
+        # best-of-candidates per shape (a stronger baseline than the cost model's pick)
+        best = {}
+        buffers = {"qkv": stack.qkv, "o": stack.h, "gate_up": stack.gu, "down": stack.h}
+        for name, (k, n) in SHAPES.items():
+            cand = (C.c_int * (4 * 256))()
+            count = lib.ttsref_candidates(rows, n, k, 0, 0, I8, 48 << 10, 8 << 20, cand, 256)
+            xq = stack.q_hidden if k == HIDDEN else stack.q_ffn
+            xq.values.random_(0, 255)
+            xq.scales.fill_(0.01)
+            timings = []
+            for c in range(min(count, 256)):
+                path = tuple(cand[4 * c:4 * c + 4])
+                try:
+                    ws = [stack.weights[i][name] for i in range(min(LAYERS, 8))]
+                    for w in ws:
+                        gemm(path, xq, w, buffers[name], k, n)
+                    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    start.record(stream)
+                    for _ in range(2):
+                        for w in ws:
+                            gemm(path, xq, w, buffers[name], k, n)
+                    stop.record(stream)
+                    stop.synchronize()
+                    timings.append((start.elapsed_time(stop), path))
+                except RuntimeError:
+                    continue
+            best[name] = min(timings)[1]
+
+        def decode_step(gemm_only=False):
+            h = stack.h
+            n_res = rows * HIDDEN
+            for layer in stack.weights:
+                if not gemm_only:
+                    quantize(h, stack.q_hidden)
+                gemm(best["qkv"], stack.q_hidden, layer["qkv"], stack.qkv, HIDDEN, QKV)
+                if not gemm_only:
+                    quantize(stack.qkv[:, :HIDDEN], stack.q_hidden)
+                gemm(best["o"], stack.q_hidden, layer["o"], h, HIDDEN, HIDDEN)
+                lib.ttsref_residual_add_f32(h.data_ptr(), stack.residual.data_ptr(), n_res, sp)
+                if not gemm_only:
+                    quantize(h, stack.q_hidden)
+                gemm(best["gate_up"], stack.q_hidden, layer["gate_up"], stack.gu, HIDDEN, 2 * FFN)
+                if not gemm_only:
+                    rc = lib.ttsref_quantized_gated(stack.gu.data_ptr(), rows, FFN, BF16, stack.q_ffn.values.data_ptr(),
+                                                    stack.q_ffn.scales.data_ptr(), I8, 0, 0, 0, props.multi_processor_count,
+                                                    1, sp)
+                    assert rc == 0, lib.ttsref_last_error()
+                gemm(best["down"], stack.q_ffn, layer["down"], h, FFN, HIDDEN)
+                lib.ttsref_residual_add_f32(h.data_ptr(), stack.residual.data_ptr(), n_res, sp)
+
+        stack.h.copy_(stack.x)
+        decode_step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            decode_step()
+        gemm_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gemm_graph, stream=stream):
+            decode_step(gemm_only=True)
+    result = time_steps(args, torch, dist, world, device, stream, stack, graph, gemm_graph)
+    result["paths"] = {k: list(v) for k, v in best.items()}
+    return result
+
+
+def run_reference_cpu(args):
+    base = cpu_baseline(STREAMS)
+    line = {"impl": "reference", "metric": "quantized_linear_algorithmic_GBps", "value": base["value"], "unit": "GB/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": workload_config(STREAMS, 1),
+            "cpu_baseline": base, "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_config(rows, world):
+    return {"workload": "c5_decoder_stack28_int8_decode (shapes of c2: QKV 2048->4096, O 2048->2048, gate+up 2048->12288, "
+                        "down 6144->2048; fp32 residual on O and down)",
+            "layers": LAYERS, "streams_total": STREAMS, "rows_per_gpu": rows, "parallelism": f"dp{world} (replicated weights, no collective)",
+            "l2": "inputs larger than L2: 1.41 GB of distinct weights per step vs 126 MB L2", "timing": "CUDA events on the launch stream, CUDA-graph replay"}
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="b200q", choices=["b200q", "reference", "reference-cpu"])
+    parser.add_argument("--no-sweep", action="store_true", help="skip the per-shape extras (decode sweep, prefill, K-group)")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    args.warmup = max(3, args.warmup)
+
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference-cpu":
+        if rank == 0:
+            run_reference_cpu(args)
+        return
+    import torch
+    dist = None
+    if not torch.cuda.is_available():
+        if args.impl == "reference" and rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "no CUDA device: the reference's only implementation of this path is CUDA"}))
+            return
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    if STREAMS % world:
+        raise SystemExit("the 64 streams must divide over the GPUs")
+    rows = STREAMS // world
+    peaks = measured_peaks()
+
+    if args.impl == "reference":
+        result = run_reference(args, torch, dist, rank, world, device)
+        extras = {}
+        if result is None:
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libttsref.so (the reference's CUDA kernels) is not built"}))
+            return
+    else:
+        result, extras = run_b200q(args, torch, dist, rank, world, device)
+
+    if rank == 0:
+        total_bytes = step_bytes(rows) * world  # every GPU streams its own replica
+        ms_step = result["ms_value"] / args.steps
+        ms_e2e = result["ms_e2e"] / args.steps
+        ms_gemm = result["ms_gemm"] / args.steps
+        gemm_bytes = step_bytes(rows, gemm_only=True)
+        achieved = gemm_bytes / (ms_gemm * 1e-3) / 1e9
+        line = {
+            "metric": "quantized_linear_algorithmic_GBps", "value": round(total_bytes / (ms_step * 1e-3) / 1e9, 2), "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": workload_config(rows, world),
+            "tops": round(step_ops(rows) * world / (ms_step * 1e-3) / 1e12, 2),
+            "tokens_per_s": round(STREAMS / (ms_step * 1e-3), 1),
+            "e2e": {"value": round(total_bytes / (ms_e2e * 1e-3) / 1e9, 2), "unit": "GB/s", "ms_per_step": round(ms_e2e, 4),
+                    "h2d_bytes_per_step": result["h2d"], "d2h_bytes_per_step": result["d2h"]},
+            "roofline": {"bound": "hbm", "kernel": "w8a8 GEMM launches of one step (112 launches, 4 shapes)",
+                         "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / peaks["hbm_gbs"], 4), "frac_of_nominal_8TBps": round(achieved / 8000.0, 4),
+                         "peak_source": peaks["source"], "avg_launch_us": round(ms_gemm * 1e3 / (LAYERS * 4), 3),
+                         "algorithmic_bytes_per_launch": gemm_bytes // (LAYERS * 4), "traffic": None},
+            "clocks": result["clocks"],
+        }
+        if args.impl == "reference":
+            line["impl"] = "reference"
+            line["reference_paths"] = result.get("paths")
+            line["cpu_baseline"] = {"value": line["value"], "unit": "GB/s", "cores": 0, "kind": "reference",
+                                    "sample": "the reference's own CUDA kernels on this GPU (it has no CPU implementation of the path)"}
+            line["roofline"]["kernel"] = "reference GEMM launches of one step (+ its residual pass)"
+        else:
+            line["impl"] = "b200q"
+            line["gpu_launches"] = result["gpu_launches"]
+            if world == 1 and not args.no_cpu_baseline:
+                line["cpu_baseline"] = cpu_baseline(rows)
+            line.update(extras)
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
