@@ -490,9 +490,10 @@ def main():
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
+    from breeze_tts_cpp_b200.sharding import shard_streams
     if STREAMS % world:
         raise SystemExit("the 64 streams must divide over the GPUs")
-    rows = STREAMS // world
+    rows = shard_streams(STREAMS, world, rank)[1]
     peaks = measured_peaks()
 
     if args.impl == "reference":

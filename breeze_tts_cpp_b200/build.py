@@ -52,7 +52,7 @@ def _compile(nvcc: str, source: str, flags: list[str], header_stamp: float, verb
     if obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, header_stamp):
         return obj
     cmd = [nvcc, "-std=c++17", "-O3", *ARCH, "-lineinfo", "-Xcompiler", "-fPIC", f"-I{CSRC}", f"-I{INCLUDE}",
-           *flags, "-c", str(src), "-o", str(obj)]
+           *flags, *os.environ.get("B200Q_NVCC_FLAGS", "").split(), "-c", str(src), "-o", str(obj)]
     if verbose:
         print(" ".join(cmd), flush=True)
     done = subprocess.run(cmd, capture_output=True, text=True)

@@ -9,6 +9,7 @@
 // CTAs for short batches; with one scale per row the CTA holds the whole row (K <= 8192).
 #include "kernels/quant_gated.h"
 #include "kernels/quant_codec.cuh"
+#include "kernels/launch.cuh"
 #include <stdexcept>
 #include <string>
 
@@ -33,6 +34,8 @@ __global__ void __launch_bounds__(kThreads)
 gated_quantize(const T *__restrict__ input, unsigned char *__restrict__ out, float *__restrict__ scales, int rows,
                int cols, int group, int parts, bool aligned) {
     __shared__ float slots[kThreads / 32];
+    pdl_launch_dependents();
+    pdl_wait_upstream();
     const int row = blockIdx.x / parts, shard = blockIdx.x % parts;
     const T *gate = input + size_t(row) * cols * 2, *up = gate + cols;
     float v[Items][8];
@@ -65,7 +68,9 @@ void launch_items(const T *x, unsigned char *q, float *s, int rows, int cols, in
         while (parts < chunks && int64_t(rows) * parts * 2 <= sms) parts *= 2;
     const int items = (chunks + parts - 1) / parts;
     const unsigned grid = unsigned(rows) * unsigned(parts);
-#define B200Q_RUN(I) gated_quantize<F, T, Kind, I, Rotate><<<grid, kThreads, 0, stream>>>(x, q, s, rows, cols, group, parts, aligned)
+#define B200Q_RUN(I)                                                                                                  \
+    launch_pdl("quantized gated launch", gated_quantize<F, T, Kind, I, Rotate>, dim3(grid), dim3(kThreads), 0, stream, x, \
+               q, s, rows, cols, group, parts, aligned)
     switch (items) {
     case 1: B200Q_RUN(1); break;
     case 2: B200Q_RUN(2); break;

@@ -5,6 +5,7 @@
 #include "kernels/quant_linear_sm100.cuh"
 #include "ops/epilogue.h"
 #include <cuda.h>
+#include <cstdlib>
 #include <cudaTypedefs.h>
 #include <map>
 #include <mutex>
@@ -15,7 +16,7 @@
 namespace tts {
 namespace {
 using namespace b200;
-constexpr size_t kSmemBudget = 226 * 1024; // dynamic part; the kernel adds ~0.3 KB of static barriers (227 KB per CTA is the limit)
+constexpr size_t kSmemBudget = 208 * 1024; // dynamic part per CTA; leaves room on the SM for a co-resident producer CTA of the next kernel
 
 void check(cudaError_t status, const char *what) {
     if (status != cudaSuccess)
@@ -66,23 +67,57 @@ const CUtensorMap &tensor_map(const void *base, int rows, int k, int box_rows, b
 template <Type F, bool Grouped, int BN> auto kernel_of() { return w8a8_tcgen05_gemm<F, Grouped, BN>; }
 
 struct Shape {
-    int stages;
-    size_t smem;
+    int stages, owned_passes;
+    size_t tile_region, smem;
 };
-Shape shape_for(int bn, bool grouped, int kb_per_split) {
-    size_t stage = size_t(kBlockChannels + bn) * kBlockK;
-    size_t scales = grouped ? size_t(kb_per_split) * (bn + kBlockChannels) * sizeof(float) : 0;
-    if (1024 + scales + 2 * stage > kSmemBudget)
-        throw std::invalid_argument("quantized GEMM: K-group scales of one split exceed shared memory; use more splits");
-    int stages = int((kSmemBudget - 1024 - scales) / stage);
+// Shared memory of one CTA: alignment slack + pipeline stages (unsplit: later the transposed
+// [token][channel] tile of 4-byte partials) + split-K slots the cluster peers push into +
+// K-group scales of the CTA's K range.
+Shape shape_for(int bn, bool grouped, int kb_per_split, int splits) {
+    const size_t stage = size_t(kBlockChannels + bn) * kBlockK;
+    const size_t transposed = splits == 1 ? size_t(bn) * kBlockChannels * sizeof(float) : 0;
+    const int passes = (bn + kRowsPerPass - 1) / kRowsPerPass;
+    const int owned = splits > 1 ? (passes + splits - 1) / splits : 0;
+    const size_t reduce = size_t(splits > 1 ? splits : 0) * owned * kRowsPerPass * kBlockChannels * sizeof(float);
+    const size_t scales = grouped ? size_t(kb_per_split) * (bn + kBlockChannels) * sizeof(float) : 0;
+    const size_t fixed = 1024 + reduce + scales;
+    if (fixed + std::max(2 * stage, transposed) > kSmemBudget)
+        throw std::invalid_argument("quantized GEMM: this tile/split combination exceeds shared memory; use more splits");
+    int stages = int((kSmemBudget - fixed) / stage);
     stages = std::max(2, std::min({stages, kMaxStages, std::max(2, kb_per_split)}));
-    return {stages, 1024 + scales + size_t(stages) * stage};
+#ifdef B200Q_TIMING
+    if (const char *forced = std::getenv("B200Q_STAGES")) stages = std::max(2, std::min(stages, std::atoi(forced)));
+#endif
+    const size_t region = std::max(size_t(stages) * stage, transposed);
+    return {stages, owned, region, fixed + region};
 }
 
+// Split-K launches group the `splits` CTAs of one output tile into a thread-block cluster (1,1,splits).
 template <Type F, bool Grouped, int BN>
 void launch_instance(const CUtensorMap &map_w, const CUtensorMap &map_x, const GemmArgs &args, dim3 grid,
                      size_t smem, cudaStream_t stream) {
-    w8a8_tcgen05_gemm<F, Grouped, BN><<<grid, kGemmThreads, smem, stream>>>(map_w, map_x, args);
+    cudaLaunchConfig_t config{};
+    config.gridDim = grid;
+    config.blockDim = dim3(kGemmThreads);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    unsigned count = 0;
+    // Programmatic dependent launch: the prologue and the weight prefetch may overlap the upstream
+    // kernel; the kernel itself waits before touching anything upstream produces.
+    attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+    if (args.splits > 1) {
+        attributes[count].id = cudaLaunchAttributeClusterDimension;
+        attributes[count].val.clusterDim.x = 1;
+        attributes[count].val.clusterDim.y = 1;
+        attributes[count].val.clusterDim.z = unsigned(args.splits);
+        ++count;
+    }
+    config.attrs = attributes;
+    config.numAttrs = count;
+    check(cudaLaunchKernelEx(&config, w8a8_tcgen05_gemm<F, Grouped, BN>, map_w, map_x, args), "quantized GEMM launch");
 }
 template <Type F, bool Grouped>
 void launch_tokens(int bn, const CUtensorMap &map_w, const CUtensorMap &map_x, const GemmArgs &args, dim3 grid,
@@ -145,14 +180,12 @@ int quant_linear_status(const void *workspace, cudaStream_t stream) {
     return status;
 }
 
-size_t quant_linear_workspace_bytes(LinearPath path, KernelProblem p) {
-    if (path.splits <= 1) return kWorkspaceHeader;
-    size_t tiles = size_t((p.channels + kBlockChannels - 1) / kBlockChannels) * ((p.rows + path.tokens - 1) / path.tokens);
-    return kWorkspaceHeader + tiles * path.splits * path.tokens * kBlockChannels * sizeof(float);
-}
+// Split-K partials live in shared memory, so every path needs only the status header.
+size_t quant_linear_workspace_bytes(LinearPath, KernelProblem) { return kWorkspaceHeader; }
 
 LinearPath select_tcgen05_path(KernelProblem p, Type format, int sms, size_t workspace_bytes) {
     (void)format;
+    (void)workspace_bytes; // the GEMM keeps its split-K partials in shared memory
     if (sms <= 0) sms = 148;
     const bool grouped = p.input_group || p.weight_group;
     const int max_tokens = grouped ? 128 : 256;
@@ -163,25 +196,25 @@ LinearPath select_tcgen05_path(KernelProblem p, Type format, int sms, size_t wor
     const int64_t tiles = int64_t(n_tiles) * m_tiles;
     const int kb_total = (p.reduction + kBlockK - 1) / kBlockK;
     LinearPath best{LinearKind::Tcgen05, bn, kBlockChannels, 1};
-    if (tiles > 4096) return best; // ticket table bound; such grids fill the machine anyway
-    // Cost in "K blocks streamed by the busiest SM", plus a fixed per-CTA prologue/epilogue and
-    // the split reduction. Memory-bound shapes want every SM to stream a disjoint weight slab.
+    // Cost in "K blocks streamed by the busiest SM" plus a fixed per-CTA prologue/epilogue, with the
+    // split reduction growing with the tile it moves through shared memory. Memory-bound shapes want
+    // every SM to stream a disjoint weight slab; clusters of `splits` CTAs must fit the machine.
     double best_cost = 1e300;
-    for (int splits = 1; splits <= std::min(kb_total, 32); ++splits) {
-        LinearPath candidate{LinearKind::Tcgen05, bn, kBlockChannels, splits};
-        if (quant_linear_workspace_bytes(candidate, p) > workspace_bytes) break;
-        if (grouped) {
-            int per_split = (kb_total + splits - 1) / splits;
-            if (1024 + size_t(per_split) * (bn + kBlockChannels) * 4 + 2 * size_t(kBlockChannels + bn) * kBlockK > kSmemBudget)
-                continue;
+    for (int splits = 1; splits <= std::min(kb_total, kMaxSplits); ++splits) {
+        const int per_split = (kb_total + splits - 1) / splits;
+        try {
+            shape_for(bn, grouped, per_split, splits);
+        } catch (const std::invalid_argument &) {
+            continue;
         }
-        int64_t ctas = tiles * splits;
-        double waves = double((ctas + sms - 1) / sms);
-        double per_cta = double((kb_total + splits - 1) / splits) + 6.0 + (splits > 1 ? 2.0 + 0.25 * splits * bn / 16.0 : 0.0);
-        double cost = waves * per_cta;
+        const int64_t ctas = tiles * splits;
+        const int slots = sms / splits * splits; // whole clusters only
+        const double waves = double((ctas + slots - 1) / slots);
+        const double per_cta = double(per_split) + 6.0 + (splits > 1 ? 1.0 + bn / 32.0 : 0.0);
+        const double cost = waves * per_cta;
         if (cost < best_cost - 1e-9) {
             best_cost = cost;
-            best = candidate;
+            best = LinearPath{LinearKind::Tcgen05, bn, kBlockChannels, splits};
         }
     }
     return best;
@@ -206,27 +239,20 @@ void launch_quant_linear(LinearPath config, KernelProblem shape, const void *inp
     if (!input || !xs || !weights || !ws || !y) throw std::invalid_argument("quantized GEMM null operand");
     const int kb_total = (shape.reduction + kBlockK - 1) / kBlockK;
     const int bn = config.tokens, splits = config.splits;
-    if (config.channels != kBlockChannels || splits < 1 || splits > kb_total)
-        throw std::invalid_argument("invalid tcgen05 tile or split");
+    if (config.channels != kBlockChannels || splits < 1 || splits > kb_total || splits > kMaxSplits)
+        throw std::invalid_argument("invalid tcgen05 tile or split (splits form a cluster of at most 8 CTAs)");
     const int n_tiles = (shape.channels + kBlockChannels - 1) / kBlockChannels, m_tiles = (shape.rows + bn - 1) / bn;
     if (m_tiles > 65535 || splits > 65535) throw std::invalid_argument("quantized GEMM grid exceeds capacity");
     if (!workspace || bytes < kWorkspaceHeader) throw std::invalid_argument("quantized GEMM workspace missing");
-    if (splits > 1) {
-        if (size_t(n_tiles) * m_tiles > kTicketBytes / sizeof(int))
-            throw std::invalid_argument("too many tiles for split-K tickets");
-        if (quant_linear_workspace_bytes(config, shape) > bytes)
-            throw std::invalid_argument("quantized GEMM partial workspace overflow");
-    }
 
     GemmArgs args{};
     args.m = shape.rows; args.n = shape.channels; args.k = shape.reduction;
     args.sx = xs; args.sw = ws; args.out = y; args.out_type = int(output_type);
     args.input_group = shape.input_group; args.weight_group = shape.weight_group;
     args.splits = splits;
-    char *base = static_cast<char *>(workspace);
-    args.tickets = reinterpret_cast<int *>(base);
-    args.status = reinterpret_cast<int *>(base + kStatusOffset);
-    args.partials = reinterpret_cast<float *>(base + kWorkspaceHeader);
+    args.status = reinterpret_cast<int *>(static_cast<char *>(workspace) + kStatusOffset);
+    auto aligned16 = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    bool vector_io = aligned16(y) && shape.channels % 8 == 0;
     if (finish) {
         const auto &e = *finish;
         if (!ops::fusable(e)) throw std::invalid_argument("unsupported quantized native Finish path");
@@ -246,9 +272,13 @@ void launch_quant_linear(LinearPath config, KernelProblem shape, const void *inp
         args.ep.activation = int(e.activation);
         args.ep.chain = e.bias.data || e.residual.data || e.value_scale != 1.f || e.output_scale != 1.f ||
                         e.activation != ops::Activation::Identity;
+        vector_io = vector_io && aligned16(e.residual_f32.data);
     }
-    const Shape launch = shape_for(bn, grouped, (kb_total + splits - 1) / splits);
+    args.vector_io = vector_io;
+    const Shape launch = shape_for(bn, grouped, (kb_total + splits - 1) / splits, splits);
     args.stages = launch.stages;
+    args.tile_region = int(launch.tile_region);
+    args.owned_passes = launch.owned_passes;
     const CUtensorMap &map_w = tensor_map(weights, shape.channels, shape.reduction, kBlockChannels, true);
     const CUtensorMap &map_x = tensor_map(input, shape.rows, shape.reduction, bn, false);
     dim3 grid(n_tiles, m_tiles, splits);
@@ -259,7 +289,6 @@ void launch_quant_linear(LinearPath config, KernelProblem shape, const void *inp
         if (grouped) launch_tokens<Type::FP8, true>(bn, map_w, map_x, args, grid, launch.smem, stream);
         else launch_tokens<Type::FP8, false>(bn, map_w, map_x, args, grid, launch.smem, stream);
     }
-    check(cudaGetLastError(), "quantized GEMM launch");
 }
 
 void grouped_quant_gemm(KernelProblem problem, const void *input, const float *input_scales,

@@ -13,10 +13,19 @@
 //                    (reference: src/ops/kernels/quant/quant_grouped.cu:85-168); every K block
 //                    accumulates into a fresh tensor-memory buffer that the epilogue warps drain
 //                    and rescale while the next block's MMAs run.
-//   split-K        : every split writes its partial tile to the workspace; the last one to arrive
-//                    (an atomic ticket, no spinning) sums the partials in split order and runs the
-//                    epilogue, then resets the ticket
-//                    (replaces reference quant_reduce.cuh:9-29, a second launch).
+//   split-K        : the splits of one output tile form a thread-block cluster. Token rows are dealt
+//                    to the CTAs in blocks of 16; every CTA pushes its partial rows straight from
+//                    tensor memory into the owner's shared memory (one slot per split, remote
+//                    stores over distributed shared memory), one cluster barrier later the owner
+//                    sums its slots in split order and finishes the rows. No workspace traffic, no
+//                    second launch (replaces reference quant_reduce.cuh:9-29), deterministic.
+//   launch overlap : the kernel starts under programmatic dependent launch: barriers, tensor
+//                    memory and the first pipeline stages of WEIGHT tiles are set up while the
+//                    producer of the activations is still running; only the activation tiles, the
+//                    scales and the residual wait for it.
+//   epilogue       : accumulators leave tensor memory lane-per-channel, are transposed through
+//                    shared memory, and are finished token-row-wise so that every global access
+//                    (fp32 residual, bias, bf16 store) is a coalesced 16-byte vector.
 #pragma once
 #include "kernels/sm100_ptx.cuh"
 #include "core/tensor.h"
@@ -28,12 +37,16 @@ namespace tts::b200 {
 constexpr int kBlockChannels = 128; // MMA M: weight rows per tile
 constexpr int kBlockK = 128;        // bytes of K per pipeline stage (one 128B-swizzled TMA box)
 constexpr int kMaxStages = 12;
-constexpr int kGemmThreads = 192;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2-5 epilogue
+constexpr int kGemmThreads = 320;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2-9 epilogue
+constexpr int kEpilogueThreads = 256;
+constexpr int kRowsPerPass = 16;    // token rows the epilogue warps finish per pass (16 threads x 8 channels per row)
 
-// Workspace carve-up (owner zeroes the first kWorkspaceHeader bytes once):
-constexpr size_t kTicketBytes = 16384;     // int tickets, one per output tile
+constexpr int kMaxSplits = 8;       // portable thread-block cluster size
+
+// Workspace carve-up (owner zeroes the first kWorkspaceHeader bytes once). The GEMM itself needs
+// no scratch; only the status word lives here.
 constexpr size_t kStatusOffset = 16384;    // int status[4]: nonzero after a bounded wait gave up
-constexpr size_t kWorkspaceHeader = 32768; // split-K partials start here
+constexpr size_t kWorkspaceHeader = 32768;
 
 struct FusedEpilogue {
     const void *bias = nullptr;         // [N], output dtype
@@ -45,6 +58,12 @@ struct FusedEpilogue {
     int chain = 0;                      // nonzero when anything beyond residual_f32 is requested
 };
 
+#ifdef B200Q_TIMING
+#define B200Q_STAMP(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { long long t_; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_) :: "memory"); reinterpret_cast<long long *>(a.status + 16)[slot] = t_; } } while (0)
+#else
+#define B200Q_STAMP(slot) do { } while (0)
+#endif
+
 struct GemmArgs {
     int m, n, k;
     const float *sx, *sw;
@@ -52,8 +71,9 @@ struct GemmArgs {
     int out_type; // Type::BF16, Type::F16, or Type::I32 (raw accumulators, per-row INT8 only)
     int input_group, weight_group;
     int splits, stages;
-    float *partials; // 4-byte partial sums (int32 bit patterns or fp32)
-    int *tickets;
+    int tile_region; // bytes of shared memory holding the pipeline stages (and, unsplit, the transposed tile)
+    int owned_passes; // split-K: 16-row passes each CTA of the cluster may own (slots per split)
+    int vector_io;   // every global row touched by the epilogue is 16-byte aligned
     int *status;
     FusedEpilogue ep;
 };
@@ -79,58 +99,74 @@ __device__ __forceinline__ float activate(float x, int kind, float alpha) {
     }
 }
 
-// Dequantized fp32 value -> stored element, with the optional chain whose rounding points follow
-// the reference's post-GEMM pass (src/ops/kernels/sequence/sequence_internal.cuh:52-74).
-__device__ __forceinline__ void store_output(const GemmArgs &a, float value, int m, int n) {
-    const size_t at = size_t(m) * a.n + n;
-    const FusedEpilogue &e = a.ep;
-    if (e.residual_f32) value = __fadd_rn(value, e.residual_f32[at]);
-    if (e.chain) {
-        const int t = a.out_type;
-        value = round_to(value, t);
-        if (e.bias) value = round_to(__fadd_rn(value, load_as(e.bias, n, t)), t);
-        if (e.residual || e.value_scale != 1.f) {
-            float skip = e.residual ? load_as(e.residual, size_t(m) * e.residual_ld + n, t) : 0.f;
-            value = round_to(__fadd_rn(__fmul_rn(e.value_scale, value), __fmul_rn(e.residual_scale, skip)), t);
-        }
-        if (e.activation || e.output_scale != 1.f)
-            value = activate(round_to(__fmul_rn(value, e.output_scale), t), e.activation, e.alpha);
+// Post-GEMM chain on one rounded value; rounding points follow the reference's separate pass
+// (src/ops/kernels/sequence/sequence_internal.cuh:52-74). `bias` and `skip` are already fp32
+// (0 when absent). Deliberately not inlined: the transcendental activations are large, and eight
+// inlined copies per row pushed the common no-chain path out of the instruction cache.
+__device__ __noinline__ float finish_chain(const FusedEpilogue &e, int type, float value, float bias, float skip) {
+    value = round_to(value, type);
+    if (e.bias) value = round_to(__fadd_rn(value, bias), type);
+    if (e.residual || e.value_scale != 1.f)
+        value = round_to(__fadd_rn(__fmul_rn(e.value_scale, value), __fmul_rn(e.residual_scale, skip)), type);
+    if (e.activation || e.output_scale != 1.f)
+        value = activate(round_to(__fmul_rn(value, e.output_scale), type), e.activation, e.alpha);
+    return value;
+}
+__device__ __forceinline__ uint32_t pack16(float lo, float hi, int type) {
+    if (type == int(Type::F16)) {
+        __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t *>(&h);
     }
-    if (a.out_type == int(Type::F16)) static_cast<__half *>(a.out)[at] = __float2half_rn(value);
-    else static_cast<__nv_bfloat16 *>(a.out)[at] = __float2bfloat16_rn(value);
+    __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&b);
 }
 
 template <Type F, bool Grouped, int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads, (!Grouped && BN <= 64) ? 2 : 1)
 w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                   const GemmArgs a) {
     constexpr bool kInt = F == Type::I8;
-    constexpr bool kIntAcc = kInt && !Grouped; // partials / raw outputs carry int32 bit patterns
+    constexpr bool kIntAcc = kInt && !Grouped; // partial tiles / raw outputs carry int32 bit patterns
     constexpr int kWeightBytes = kBlockChannels * kBlockK, kTokenBytes = BN * kBlockK;
     constexpr int kStageBytes = kWeightBytes + kTokenBytes;
     constexpr int kAccColumns = Grouped ? 2 * BN : BN;
     constexpr uint32_t kTmemColumns = kAccColumns <= 32 ? 32 : kAccColumns <= 64 ? 64 : kAccColumns <= 128 ? 128
                                       : kAccColumns <= 256 ? 256 : 512;
     constexpr uint32_t kIdesc = kInt ? ptx::idesc_i8(kBlockChannels, BN) : ptx::idesc_e4m3(kBlockChannels, BN);
+    constexpr int kChunks = BN / 16;               // 16-token column chunks of the accumulator
+    constexpr int kMyChunks = (kChunks + 1) / 2;   // two epilogue warps share a lane quadrant
+    constexpr uint32_t kPassBytes = kRowsPerPass * kBlockChannels * 4;
 
     extern __shared__ uint8_t dynamic_smem[];
     __shared__ alignas(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_slot;
-    __shared__ int abort_flag, last_flag;
+    __shared__ int abort_flag;
+    __shared__ float sx_tile[BN]; // per-row activation scales of this token tile
 
+    // Dynamic shared memory, 1024-byte aligned for the swizzled TMA boxes:
+    //   [pipeline stages | split-K slots pushed by the cluster peers | K-group scales]
+    // Unsplit launches reuse the stage memory for the transposed tile once the last MMA retired;
+    // split launches must not, because peers push while this CTA may still be in its main loop.
     const uint32_t raw_base = ptx::smem_u32(dynamic_smem);
     const uint32_t tiles_base = (raw_base + 1023u) & ~1023u;
     uint8_t *tiles_ptr = dynamic_smem + (tiles_base - raw_base);
-    float *scale_smem = reinterpret_cast<float *>(tiles_ptr + size_t(a.stages) * kStageBytes);
+    const int splits = a.splits;
+    const uint32_t reduce_bytes = splits > 1 ? uint32_t(splits * a.owned_passes) * kPassBytes : 0u;
+    const uint32_t reduce_base = tiles_base + uint32_t(a.tile_region);
+    uint8_t *reduce_ptr = tiles_ptr + a.tile_region;
+    float *scale_smem = reinterpret_cast<float *>(reduce_ptr + reduce_bytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kBlockChannels, m0 = blockIdx.y * BN, split = blockIdx.z;
+    const int split = splits > 1 ? int(ptx::cluster_ctarank()) : 0; // cluster = (1,1,splits): rank == blockIdx.z
+    const int n0 = blockIdx.x * kBlockChannels, m0 = blockIdx.y * BN;
     const int kb_total = (a.k + kBlockK - 1) / kBlockK;
-    const int kb_begin = int(int64_t(kb_total) * split / a.splits);
-    const int kb_end = int(int64_t(kb_total) * (split + 1) / a.splits);
+    const int kb_begin = int(int64_t(kb_total) * split / splits);
+    const int kb_end = int(int64_t(kb_total) * (split + 1) / splits);
     const int kb_count = kb_end - kb_begin;
     const int tile_linear = blockIdx.y * gridDim.x + blockIdx.x;
+    const int valid_tokens = min(BN, a.m - m0);
 
+    if (threadIdx.x == 0) B200Q_STAMP(0);
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
@@ -138,10 +174,9 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(ptx::smem_u32(&acc_full[b]), 1);
-            ptx::mbar_init(ptx::smem_u32(&acc_empty[b]), 4);
+            ptx::mbar_init(ptx::smem_u32(&acc_empty[b]), kEpilogueThreads / 32);
         }
         abort_flag = 0;
-        last_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async_smem();
     }
@@ -151,15 +186,31 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     ptx::tcgen05_fence_after();
     const uint32_t tmem_base = tmem_slot;
     volatile int *abort_ptr = &abort_flag;
+    // The next kernel in the stream may begin its own prologue; peers learn that this CTA is running.
+    ptx::launch_dependents();
+    if (splits > 1) ptx::cluster_arrive();
+    if (threadIdx.x == 0) B200Q_STAMP(1);
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             ptx::prefetch_tensormap(&map_w);
             ptx::prefetch_tensormap(&map_x);
-            int stage = 0;
-            uint32_t phase = 0;
-            for (int kb = kb_begin; kb < kb_end; ++kb) {
+            // Weights do not depend on the upstream kernel: fill the ring with weight tiles first,
+            // then wait for upstream and add the activation tiles to the same stages.
+            const int ahead = min(a.stages, kb_count);
+            for (int i = 0; i < ahead; ++i) {
+                const uint32_t bar = ptx::smem_u32(&full_bar[i]);
+                ptx::mbar_arrive_expect_tx(bar, kStageBytes);
+                ptx::tma_load_2d(tiles_base + uint32_t(i) * kStageBytes, &map_w, bar, (kb_begin + i) * kBlockK, n0);
+            }
+            ptx::wait_for_upstream();
+            for (int i = 0; i < ahead; ++i)
+                ptx::tma_load_2d(tiles_base + uint32_t(i) * kStageBytes + kWeightBytes, &map_x,
+                                 ptx::smem_u32(&full_bar[i]), (kb_begin + i) * kBlockK, m0);
+            int stage = ahead == a.stages ? 0 : ahead;
+            uint32_t phase = ahead == a.stages ? 1u : 0u;
+            for (int kb = kb_begin + ahead; kb < kb_end; ++kb) {
                 if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_ptr)) break;
                 const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
                 const uint32_t dst = tiles_base + uint32_t(stage) * kStageBytes;
@@ -169,6 +220,7 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 if (++stage == a.stages) { stage = 0; phase ^= 1u; }
             }
         }
+        if (splits > 1) ptx::cluster_wait();
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
@@ -179,6 +231,7 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 if (Grouped && !ptx::mbar_wait(ptx::smem_u32(&acc_empty[buffer]), ((uint32_t(it) >> 1) & 1u) ^ 1u, abort_ptr))
                     break;
                 if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_ptr)) break;
+                if (it == 0) B200Q_STAMP(2);
                 ptx::tcgen05_fence_after();
                 const uint32_t tile = tiles_base + uint32_t(stage) * kStageBytes;
                 const uint64_t desc_w = ptx::smem_desc_k128(tile), desc_x = ptx::smem_desc_k128(tile + kWeightBytes);
@@ -195,67 +248,103 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 if (++stage == a.stages) { stage = 0; phase ^= 1u; }
             }
             if (!Grouped) ptx::tcgen05_commit(ptx::smem_u32(&acc_full[0]));
+            B200Q_STAMP(3);
         }
+        if (splits > 1) ptx::cluster_wait();
     } else {
-        // ------------------------------------------------------------ epilogue warps
-        const int quadrant = warp & 3;             // tensor-memory lanes this warp may read
+        // ------------------------------------------------------------ epilogue warps (8 warps)
+        const int e_thread = threadIdx.x - 64;
+        const int quadrant = warp & 3;      // tensor-memory lanes this warp may read
+        const int half = (warp - 2) >> 2;   // the two warps of a quadrant take alternate 16-token chunks
         const int channel_in_tile = quadrant * 32 + lane;
-        const int n = n0 + channel_in_tile;
-        const int epi_thread = threadIdx.x - 64;
         const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16);
-        const int valid_tokens = min(BN, a.m - m0);
-        const bool channel_ok = n < a.n;
-        float *my_partials = a.partials + (size_t(tile_linear) * a.splits + split) * BN * kBlockChannels;
+        uint32_t *tile_words = reinterpret_cast<uint32_t *>(tiles_ptr);
         bool ok = true;
 
+        // Phase-2 ownership of this thread: 8 consecutive channels of one token row per pass.
+        const int j = e_thread & 15, row_in_pass = e_thread >> 4;
+        const int n = n0 + 8 * j;
+        const bool columns_ok = n < a.n;
+        const FusedEpilogue &e = a.ep;
+        const int type = a.out_type;
+        const int passes = (valid_tokens + kRowsPerPass - 1) / kRowsPerPass;
+        // Static operands (weights' scales, bias) are fetched before anything else so their latency
+        // hides behind the main loop.
+        float sw8[8], bias8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            sw8[i] = (!Grouped && columns_ok) ? a.sw[n + i] : 1.f;
+            bias8[i] = (e.bias && columns_ok) ? load_as(e.bias, n + i, type) : 0.f;
+        }
+        ptx::wait_for_upstream(); // activation scales, residuals and the output buffer belong to upstream
+        float first_residual[8];
+        {
+            const int c = split * kRowsPerPass + row_in_pass; // first pass this CTA owns
+#pragma unroll
+            for (int i = 0; i < 8; ++i) first_residual[i] = 0.f;
+            if (e.residual_f32 && columns_ok && c < valid_tokens) {
+                const float *src = e.residual_f32 + size_t(m0 + c) * a.n + n;
+                if (a.vector_io) {
+                    const float4 lo = *reinterpret_cast<const float4 *>(src), hi = *reinterpret_cast<const float4 *>(src + 4);
+                    first_residual[0] = lo.x; first_residual[1] = lo.y; first_residual[2] = lo.z; first_residual[3] = lo.w;
+                    first_residual[4] = hi.x; first_residual[5] = hi.y; first_residual[6] = hi.z; first_residual[7] = hi.w;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) first_residual[i] = src[i];
+                }
+            }
+        }
+
+        // ---- phase 1: accumulators (one lane = one channel) -> [token][channel] rows, either in this
+        // CTA's shared memory (unsplit) or pushed into the owning peer's slot for this split.
+        auto emit_chunk = [&](int chunk, const uint32_t (&words)[16]) {
+            if (splits == 1) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    if (chunk * 16 + i < valid_tokens) tile_words[(chunk * 16 + i) * kBlockChannels + channel_in_tile] = words[i];
+            } else {
+                const int owner = chunk % splits, local_pass = chunk / splits;
+                const uint32_t slot = reduce_base + uint32_t(split * a.owned_passes + local_pass) * kPassBytes +
+                                      uint32_t(channel_in_tile) * 4u;
+                const uint32_t remote = ptx::map_to_rank(slot, uint32_t(owner));
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    if (chunk * 16 + i < valid_tokens) ptx::st_cluster_u32(remote + uint32_t(i) * (kBlockChannels * 4u), words[i]);
+            }
+        };
+
         if constexpr (!Grouped) {
+            for (int c = e_thread; c < BN; c += kEpilogueThreads) sx_tile[c] = c < valid_tokens ? a.sx[m0 + c] : 0.f;
             ok = ptx::mbar_wait(ptx::smem_u32(&acc_full[0]), 0, abort_ptr);
+            if (e_thread == 0) B200Q_STAMP(4);
             ptx::tcgen05_fence_after();
-            const float scale_w = channel_ok ? a.sw[n] : 0.f;
+            if (splits > 1) ptx::cluster_wait(); // every peer is running: its shared memory may be written
             if (ok) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    if (c0 >= valid_tokens) break;
+                for (int chunk = half; chunk < kChunks; chunk += 2) {
+                    if (chunk * 16 >= valid_tokens) break;
                     uint32_t r[16];
-                    ptx::tmem_load16(lane_base + uint32_t(c0), r);
+                    ptx::tmem_load16(lane_base + uint32_t(chunk * 16), r);
                     ptx::tmem_load_wait();
-                    if (a.splits > 1) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            if (c0 + i < valid_tokens)
-                                __stcg(reinterpret_cast<uint32_t *>(my_partials) + size_t(c0 + i) * kBlockChannels + channel_in_tile, r[i]);
-                    } else if (channel_ok) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const int m = m0 + c0 + i;
-                            if (c0 + i < valid_tokens) {
-                                if (a.out_type == int(Type::I32)) {
-                                    static_cast<uint32_t *>(a.out)[size_t(m) * a.n + n] = r[i];
-                                } else {
-                                    float acc = kInt ? float(int(r[i])) : __uint_as_float(r[i]);
-                                    store_output(a, __fmul_rn(__fmul_rn(acc, a.sx[m]), scale_w), m, n);
-                                }
-                            }
-                        }
-                    }
+                    emit_chunk(chunk, r);
                 }
             }
         } else {
             // Stage this split's group scales once: sx_g[block][token], sw_g[block][channel].
             float *sx_smem = scale_smem, *sw_smem = scale_smem + size_t(kb_count) * BN;
-            for (int i = epi_thread; i < kb_count * BN; i += 128) {
+            for (int i = e_thread; i < kb_count * BN; i += kEpilogueThreads) {
                 int block = i / BN, token = i % BN;
                 sx_smem[i] = (a.input_group && token < valid_tokens)
                                  ? a.sx[size_t(kb_begin + block) * a.m + m0 + token] : 1.f;
             }
-            for (int i = epi_thread; i < kb_count * kBlockChannels; i += 128) {
+            for (int i = e_thread; i < kb_count * kBlockChannels; i += kEpilogueThreads) {
                 int block = i / kBlockChannels, channel = n0 + i % kBlockChannels;
                 sw_smem[i] = (a.weight_group && channel < a.n) ? a.sw[size_t(kb_begin + block) * a.n + channel] : 1.f;
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            float result[BN];
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            float result[kMyChunks * 16];
 #pragma unroll
-            for (int c = 0; c < BN; ++c) result[c] = 0.f;
+            for (int c = 0; c < kMyChunks * 16; ++c) result[c] = 0.f;
 #pragma unroll 1
             for (int it = 0; it < kb_count && ok; ++it) {
                 const int buffer = it & 1;
@@ -264,79 +353,149 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 ptx::tcgen05_fence_after();
                 const float scale_w = sw_smem[it * kBlockChannels + channel_in_tile];
                 const float *scale_x = sx_smem + it * BN;
+                uint32_t r[kMyChunks][16];
 #pragma unroll
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    uint32_t r[16];
-                    ptx::tmem_load16(lane_base + uint32_t(buffer * BN + c0), r);
-                    ptx::tmem_load_wait();
-                    if (c0 + 16 >= BN) {
-                        // Last chunk read: hand the buffer back before doing the arithmetic.
-                        ptx::tcgen05_fence_before();
-                        __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&acc_empty[buffer]));
-                    }
+                for (int k = 0; k < kMyChunks; ++k)
+                    if (2 * k + half < kChunks) ptx::tmem_load16(lane_base + uint32_t(buffer * BN + (2 * k + half) * 16), r[k]);
+                ptx::tmem_load_wait();
+                // Everything this warp needs is in registers: hand the buffer back before the arithmetic.
+                ptx::tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&acc_empty[buffer]));
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        // |p| <= 128*127^2 < 2^24, so the int -> float conversion is exact.
-                        float p = kInt ? float(int(r[i])) : __uint_as_float(r[i]);
-                        result[c0 + i] = fmaf(p, scale_x[c0 + i] * scale_w, result[c0 + i]);
-                    }
-                }
-            }
-            if (ok) {
-                float outer_w = (!a.weight_group && channel_ok) ? a.sw[n] : 1.f;
+                for (int k = 0; k < kMyChunks; ++k) {
+                    if (2 * k + half < kChunks) {
 #pragma unroll
-                for (int c = 0; c < BN; ++c) {
-                    if (c < valid_tokens) {
-                        const int m = m0 + c;
-                        float value = result[c] * ((a.input_group ? 1.f : a.sx[m]) * outer_w);
-                        if (a.splits > 1) __stcg(my_partials + size_t(c) * kBlockChannels + channel_in_tile, value);
-                        else if (channel_ok) store_output(a, value, m, n);
-                    }
-                }
-            }
-        }
-
-        if (a.splits > 1) {
-            // Publish the partial tile, take a ticket; the last split to arrive reduces all of them.
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (epi_thread == 0) {
-                int ticket = atomicAdd(a.tickets + tile_linear, 1);
-                int last = ticket == a.splits - 1;
-                if (last) a.tickets[tile_linear] = 0; // self-resetting for the next launch / graph replay
-                last_flag = last;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (last_flag && ok && !*abort_ptr) {
-                __threadfence();
-                const float *tile_partials = a.partials + size_t(tile_linear) * a.splits * BN * kBlockChannels;
-                const float scale_w = (!Grouped && channel_ok) ? a.sw[n] : 0.f;
-                for (int c = 0; c < valid_tokens; ++c) {
-                    const int m = m0 + c;
-                    const size_t at = size_t(c) * kBlockChannels + channel_in_tile;
-                    if (kIntAcc) {
-                        int sum = 0;
-                        for (int s = 0; s < a.splits; ++s)
-                            sum += int(__ldcg(reinterpret_cast<const uint32_t *>(tile_partials) + size_t(s) * BN * kBlockChannels + at));
-                        if (channel_ok) {
-                            if (a.out_type == int(Type::I32)) static_cast<int *>(a.out)[size_t(m) * a.n + n] = sum;
-                            else store_output(a, __fmul_rn(__fmul_rn(float(sum), a.sx[m]), scale_w), m, n);
+                        for (int i = 0; i < 16; ++i) {
+                            // |p| <= 128*127^2 < 2^24, so the int -> float conversion is exact.
+                            const float p = kInt ? float(int(r[k][i])) : __uint_as_float(r[k][i]);
+                            result[k * 16 + i] = fmaf(p, scale_x[(2 * k + half) * 16 + i] * scale_w, result[k * 16 + i]);
                         }
-                    } else {
-                        float sum = 0.f;
-                        for (int s = 0; s < a.splits; ++s)
-                            sum = __fadd_rn(sum, __ldcg(tile_partials + size_t(s) * BN * kBlockChannels + at));
-                        if (channel_ok)
-                            store_output(a, Grouped ? sum : __fmul_rn(__fmul_rn(sum, a.sx[m]), scale_w), m, n);
+                    }
+                }
+            }
+            if (e_thread == 0) B200Q_STAMP(4);
+            if (splits > 1) ptx::cluster_wait();
+            if (ok) {
+                // Outer scales exist only when just one operand carries K-group scales.
+                const int channel = n0 + channel_in_tile;
+                const float outer_w = (!a.weight_group && channel < a.n) ? a.sw[channel] : 1.f;
+#pragma unroll
+                for (int k = 0; k < kMyChunks; ++k) {
+                    const int chunk = 2 * k + half;
+                    if (chunk < kChunks && chunk * 16 < valid_tokens) {
+                        uint32_t words[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int c = chunk * 16 + i;
+                            const float outer = (a.input_group || c >= valid_tokens) ? 1.f : a.sx[m0 + c];
+                            words[i] = __float_as_uint(result[k * 16 + i] * (outer * outer_w));
+                        }
+                        emit_chunk(chunk, words);
                     }
                 }
             }
         }
+        if (e_thread == 0) B200Q_STAMP(7);
         ptx::tcgen05_fence_before();
-    }
 
-    __syncthreads();
+        // ---- phase boundary: rows are where their finisher will read them.
+        if (splits > 1) ptx::cluster_sync();
+        else asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (e_thread == 0) B200Q_STAMP(8);
+
+        // ---- phase 2: finish token rows; every global access is a 16-byte vector on a 256-byte row.
+        if (ok && !*abort_ptr && columns_ok) {
+            for (int local_pass = 0;; ++local_pass) {
+                const int pass = local_pass * splits + split;
+                if (pass >= passes) break;
+                const int c = pass * kRowsPerPass + row_in_pass;
+                if (c >= valid_tokens) continue;
+                const int m = m0 + c;
+                uint32_t raw[8];
+                if (splits == 1) {
+                    const uint8_t *src = tiles_ptr + size_t(c * kBlockChannels + 8 * j) * 4;
+                    const uint4 lo = *reinterpret_cast<const uint4 *>(src), hi = *reinterpret_cast<const uint4 *>(src + 16);
+                    raw[0] = lo.x; raw[1] = lo.y; raw[2] = lo.z; raw[3] = lo.w;
+                    raw[4] = hi.x; raw[5] = hi.y; raw[6] = hi.z; raw[7] = hi.w;
+                } else {
+                    // Slots of this pass, one per split, summed in split order (deterministic).
+                    const uint8_t *src = reduce_ptr + size_t(local_pass) * kPassBytes + size_t(row_in_pass * kBlockChannels + 8 * j) * 4;
+                    const size_t slot_stride = size_t(a.owned_passes) * kPassBytes;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) raw[i] = 0u; // int 0 and +0.f share this pattern
+                    for (int s = 0; s < splits; ++s) {
+                        const uint4 lo = *reinterpret_cast<const uint4 *>(src + s * slot_stride);
+                        const uint4 hi = *reinterpret_cast<const uint4 *>(src + s * slot_stride + 16);
+                        const uint32_t part[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            raw[i] = kIntAcc ? uint32_t(int(raw[i]) + int(part[i]))
+                                             : __float_as_uint(__fadd_rn(__uint_as_float(raw[i]), __uint_as_float(part[i])));
+                    }
+                }
+                const size_t at = size_t(m) * a.n + n;
+                if (type == int(Type::I32)) {
+                    uint32_t *dst = static_cast<uint32_t *>(a.out) + at;
+                    if (a.vector_io) {
+                        *reinterpret_cast<uint4 *>(dst) = make_uint4(raw[0], raw[1], raw[2], raw[3]);
+                        *reinterpret_cast<uint4 *>(dst + 4) = make_uint4(raw[4], raw[5], raw[6], raw[7]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) dst[i] = raw[i];
+                    }
+                    continue;
+                }
+                float value[8];
+                const float scale_x = sx_tile[Grouped ? 0 : c];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float acc = kIntAcc ? float(int(raw[i])) : __uint_as_float(raw[i]);
+                    value[i] = Grouped ? acc : __fmul_rn(__fmul_rn(acc, scale_x), sw8[i]);
+                }
+                if (e.residual_f32) {
+                    float r8[8];
+                    if (local_pass == 0) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) r8[i] = first_residual[i];
+                    } else if (a.vector_io) {
+                        const float4 lo = *reinterpret_cast<const float4 *>(e.residual_f32 + at);
+                        const float4 hi = *reinterpret_cast<const float4 *>(e.residual_f32 + at + 4);
+                        r8[0] = lo.x; r8[1] = lo.y; r8[2] = lo.z; r8[3] = lo.w;
+                        r8[4] = hi.x; r8[5] = hi.y; r8[6] = hi.z; r8[7] = hi.w;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) r8[i] = e.residual_f32[at + i];
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) value[i] = __fadd_rn(value[i], r8[i]);
+                }
+                if (e.chain) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float skip = e.residual ? load_as(e.residual, size_t(m) * e.residual_ld + n + i, type) : 0.f;
+                        value[i] = finish_chain(e, type, value[i], bias8[i], skip);
+                    }
+                }
+                uint16_t *dst = static_cast<uint16_t *>(a.out) + at;
+                const uint4 packed = make_uint4(pack16(value[0], value[1], type), pack16(value[2], value[3], type),
+                                                pack16(value[4], value[5], type), pack16(value[6], value[7], type));
+                if (a.vector_io) {
+                    *reinterpret_cast<uint4 *>(dst) = packed;
+                } else {
+                    dst[0] = uint16_t(packed.x); dst[1] = uint16_t(packed.x >> 16);
+                    dst[2] = uint16_t(packed.y); dst[3] = uint16_t(packed.y >> 16);
+                    dst[4] = uint16_t(packed.z); dst[5] = uint16_t(packed.z >> 16);
+                    dst[6] = uint16_t(packed.w); dst[7] = uint16_t(packed.w >> 16);
+                }
+            }
+        }
+        if (e_thread == 0) B200Q_STAMP(5);
+    }
+    if (warp < 2 && splits > 1) ptx::cluster_sync(); // the producer/MMA warps' share of the phase barrier
+
+    __syncthreads(); // tensor memory is drained and nobody else will touch this CTA's shared memory
+    if (threadIdx.x == 0) B200Q_STAMP(6);
     if (warp == 1) {
         ptx::tcgen05_fence_after();
         ptx::tmem_dealloc(tmem_base, kTmemColumns);

@@ -9,6 +9,7 @@
 // warps; the norm uses the hardware reciprocal square root. Compile with --fmad=false.
 #include "kernels/quant_norm.h"
 #include "kernels/quant_codec.cuh"
+#include "kernels/launch.cuh"
 #include <stdexcept>
 #include <string>
 
@@ -54,12 +55,14 @@ rms_quantize(T *__restrict__ x, const T *__restrict__ update, const T *__restric
     using M = Pair16<T>;
     using P = typename M::P;
     __shared__ float slots[kThreads / 32];
+    pdl_launch_dependents();
     const int row = blockIdx.x, column = threadIdx.x * 8;
     uint4 value = make_uint4(0, 0, 0, 0), w = make_uint4(0, 0, 0, 0);
+    if (column < cols) w = load_raw8(weight + column, cols - column, aligned); // static: may precede the wait
+    pdl_wait_upstream();
     if (column < cols) {
         const int remaining = cols - column;
         value = load_raw8(x + size_t(row) * cols + column, remaining, aligned);
-        w = load_raw8(weight + column, remaining, aligned);
         if (Add) {
             uint4 u = load_raw8(update + size_t(row) * cols + column, remaining, aligned);
             uint4 s = update_scale ? load_raw8(update_scale + column, remaining, aligned) : make_uint4(0, 0, 0, 0);
@@ -121,8 +124,8 @@ void launch(T *x, const T *update, const T *weight, const T *update_scale, unsig
                          (!update || reinterpret_cast<uintptr_t>(update) % 16 == 0) &&
                          (!update_scale || reinterpret_cast<uintptr_t>(update_scale) % 16 == 0);
 #define B200Q_RUN(ADD, ROT)                                                                        \
-    rms_quantize<F, T, ADD, ROT><<<rows, kThreads, 0, stream>>>(x, update, weight, update_scale, q, s, rows, cols, \
-                                                                eps, gemma, group, aligned)
+    launch_pdl("quantized norm launch", rms_quantize<F, T, ADD, ROT>, dim3(rows), dim3(kThreads), 0, stream, x, update,   \
+               weight, update_scale, q, s, rows, cols, eps, gemma, group, aligned)
     if (update) { if (rotation) B200Q_RUN(true, true); else B200Q_RUN(true, false); }
     else { if (rotation) B200Q_RUN(false, true); else B200Q_RUN(false, false); }
 #undef B200Q_RUN

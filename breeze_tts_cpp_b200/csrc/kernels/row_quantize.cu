@@ -8,6 +8,7 @@
 // (:24-37 scalar, :42-87 register-cached, :90-115 rotated per-row, :145-165 K-group).
 #include "kernels/row_quantize.h"
 #include "kernels/quant_codec.cuh"
+#include "kernels/launch.cuh"
 #include <stdexcept>
 
 namespace tts {
@@ -21,6 +22,8 @@ __global__ void __launch_bounds__(kThreads)
 row_quantize_cached(const T *__restrict__ x, unsigned char *__restrict__ q, float *__restrict__ scales,
                     int rows, int cols, int stride, int group, int parts, bool aligned) {
     __shared__ float slots[kThreads / 32];
+    pdl_launch_dependents();
+    pdl_wait_upstream();
     const int row = blockIdx.x / parts, shard = blockIdx.x % parts;
     const T *source = x + size_t(row) * stride;
     float v[Items][8];
@@ -45,6 +48,8 @@ __global__ void __launch_bounds__(kThreads)
 row_quantize_wide(const T *__restrict__ x, unsigned char *__restrict__ q, float *__restrict__ scales,
                   int cols, int stride, bool aligned) {
     __shared__ float slots[kThreads / 32];
+    pdl_launch_dependents();
+    pdl_wait_upstream();
     const int row = blockIdx.x;
     const T *source = x + size_t(row) * stride;
     const int padded = (cols + kThreads * 8 - 1) / (kThreads * 8) * (kThreads * 8);
@@ -78,14 +83,15 @@ void launch_typed(const T *x, unsigned char *q, float *scales, int rows, int col
         while (parts < chunks && int64_t(rows) * parts * 2 <= multiprocessors) parts *= 2;
         if (chunks > 4 * parts) parts = (chunks + 3) / 4;
     } else if (chunks > 4) {
-        row_quantize_wide<F, T, Rotate><<<rows, kThreads, 0, stream>>>(x, q, scales, cols, stride, aligned);
+        launch_pdl("row quantize launch", row_quantize_wide<F, T, Rotate>, dim3(rows), dim3(kThreads), 0, stream, x, q, scales,
+                   cols, stride, aligned);
         return;
     }
     const int items = (chunks + parts - 1) / parts;
     const unsigned grid = unsigned(rows) * unsigned(parts);
 #define B200Q_LAUNCH(I)                                                                            \
-    row_quantize_cached<F, T, I, Rotate><<<grid, kThreads, 0, stream>>>(x, q, scales, rows, cols,   \
-                                                                        stride, group, parts, aligned)
+    launch_pdl("row quantize launch", row_quantize_cached<F, T, I, Rotate>, dim3(grid), dim3(kThreads), 0, stream, x, q, \
+               scales, rows, cols, stride, group, parts, aligned)
     switch (items) {
     case 1: B200Q_LAUNCH(1); break;
     case 2: B200Q_LAUNCH(2); break;

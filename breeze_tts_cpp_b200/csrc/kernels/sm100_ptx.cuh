@@ -10,11 +10,6 @@ namespace tts::b200::ptx {
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
-__device__ __forceinline__ uint64_t global_timer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
 
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -45,23 +40,70 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                  : "memory");
     return done != 0;
 }
-// Wait with a wall-clock limit. Returns false once `*abort_flag` is set by anyone or the limit
-// passes (in which case it sets the flag itself), so a wrong phase or a lost copy ends the kernel
-// with an error status instead of hanging the GPU.
-constexpr uint64_t kWaitLimitNs = 2000000000ull; // 2 s
+// Wait with a limit. Returns false once `*abort_flag` is set by anyone or the limit passes (in
+// which case it sets the flag itself), so a wrong phase or a lost copy ends the kernel with an
+// error status instead of hanging the GPU. The limit is counted on the SM's own cycle counter
+// (about two seconds at 2 GHz); the global nanosecond timer is far too slow to read in a hot loop.
+constexpr long long kWaitLimitCycles = 4000000000ll;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t start = global_timer_ns();
+    const long long start = clock64();
     for (uint32_t spin = 1;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 63u) == 0) {
+        if ((spin & 255u) == 0) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - start > kWaitLimitNs) {
+            if (clock64() - start > kWaitLimitCycles) {
                 *abort_flag = 1;
                 return false;
             }
         }
     }
+}
+
+// ---------------------------------------------------------------- thread-block clusters
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Hardware barrier over every thread of every CTA in the cluster; release/acquire makes shared
+// memory written before it visible to the peers that read it afterwards.
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Split form of the same barrier: arrive early, wait only where the peers' progress is needed.
+__device__ __forceinline__ void cluster_arrive() {
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t addr, uint32_t value) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(value) : "memory");
+}
+// Programmatic dependent launch: let the next kernel in the stream start its prologue now, and
+// block until everything the previous kernel wrote is visible. Both are no-ops for a kernel that
+// was launched without the programmatic-serialization attribute.
+__device__ __forceinline__ void launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void wait_for_upstream() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Address of the same shared-memory location in the CTA with rank `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ uint4 ld_cluster_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared::cluster.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(addr)
+                 : "memory");
+    return v;
 }
 
 // ---------------------------------------------------------------- TMA (2-D tiled load, no multicast)

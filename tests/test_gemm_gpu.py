@@ -44,7 +44,7 @@ def make_operands(oracle, m, n, k, fmt, group, rotation, seed, student_t=None):
 
 INT8_CASES = [  # m, n, k, tokens tile, splits
     (16, 128, 128, 16, 1), (16, 256, 256, 16, 1), (1, 2048, 2048, 16, 1), (3, 64, 2048, 16, 4),
-    (16, 2048, 2048, 16, 8), (17, 2048, 2048, 32, 2), (64, 4096, 2048, 64, 4), (16, 2048, 6144, 16, 16),
+    (16, 2048, 2048, 16, 8), (17, 2048, 2048, 32, 2), (64, 4096, 2048, 64, 4), (16, 2048, 6144, 16, 8), (64, 2048, 6144, 64, 7),
     (4, 12288, 2048, 16, 1), (100, 2048, 2048, 128, 3), (300, 384, 1024, 256, 1), (16, 2048, 2064, 16, 2),
 ]
 
