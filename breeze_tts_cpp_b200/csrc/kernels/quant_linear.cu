@@ -16,6 +16,7 @@
 namespace tts {
 namespace {
 using namespace b200;
+constexpr size_t kSmemCompact = 108 * 1024; // two CTAs per SM
 constexpr size_t kSmemBudget = 208 * 1024; // dynamic part per CTA; leaves room on the SM for a co-resident producer CTA of the next kernel
 
 void check(cudaError_t status, const char *what) {
@@ -83,7 +84,11 @@ Shape shape_for(int bn, bool grouped, int kb_per_split, int splits) {
     const size_t fixed = 1024 + reduce + scales;
     if (fixed + std::max(2 * stage, transposed) > kSmemBudget)
         throw std::invalid_argument("quantized GEMM: this tile/split combination exceeds shared memory; use more splits");
-    int stages = int((kSmemBudget - fixed) / stage);
+    // Weight-streaming shapes (token tiles up to 64) take at most half an SM's shared memory, so two
+    // CTAs fit per SM: the next GEMM of the stream can already be resident and prefetching its weights
+    // while this one drains, and a tile's fixed latencies overlap another tile's streaming.
+    const size_t budget = (!grouped && bn <= 64) ? std::max(kSmemCompact, fixed + std::max(2 * stage, transposed)) : kSmemBudget;
+    int stages = int((budget - fixed) / stage);
     stages = std::max(2, std::min({stages, kMaxStages, std::max(2, kb_per_split)}));
 #ifdef B200Q_TIMING
     if (const char *forced = std::getenv("B200Q_STAGES")) stages = std::max(2, std::min(stages, std::atoi(forced)));
@@ -199,19 +204,25 @@ LinearPath select_tcgen05_path(KernelProblem p, Type format, int sms, size_t wor
     // Cost in "K blocks streamed by the busiest SM" plus a fixed per-CTA prologue/epilogue, with the
     // split reduction growing with the tile it moves through shared memory. Memory-bound shapes want
     // every SM to stream a disjoint weight slab; clusters of `splits` CTAs must fit the machine.
+    // Estimated microseconds: a fixed launch/prologue/epilogue latency plus the streaming time of the
+    // busiest SM, which is bounded by what one SM can pull (about 85 GB/s) and by its share of HBM.
     double best_cost = 1e300;
-    for (int splits = 1; splits <= std::min(kb_total, kMaxSplits); ++splits) {
+    const double stage_bytes = double(kBlockChannels + bn) * kBlockK;
+    for (int splits = 1; splits <= std::min(kb_total, 4); ++splits) {
         const int per_split = (kb_total + splits - 1) / splits;
+        Shape shape{};
         try {
-            shape_for(bn, grouped, per_split, splits);
+            shape = shape_for(bn, grouped, per_split, splits);
         } catch (const std::invalid_argument &) {
             continue;
         }
+        const int per_sm = shape.smem <= kSmemCompact + 2048 ? 2 : 1;
         const int64_t ctas = tiles * splits;
-        const int slots = sms / splits * splits; // whole clusters only
+        const int64_t slots = int64_t(sms) * per_sm / splits * splits; // whole clusters only
         const double waves = double((ctas + slots - 1) / slots);
-        const double per_cta = double(per_split) + 6.0 + (splits > 1 ? 1.0 + bn / 32.0 : 0.0);
-        const double cost = waves * per_cta;
+        const double per_sm_stream = per_split * stage_bytes / 85e3;
+        const double hbm_stream = double(std::min<int64_t>(ctas, slots)) * per_split * stage_bytes / 5.5e6;
+        const double cost = 4.0 + waves * std::max(per_sm_stream, hbm_stream) + (splits > 1 ? 0.3 + 0.2 * splits : 0.0);
         if (cost < best_cost - 1e-9) {
             best_cost = cost;
             best = LinearPath{LinearKind::Tcgen05, bn, kBlockChannels, splits};
