@@ -51,6 +51,11 @@ SIGNATURES = {
     "b200q_quant_linear": (C.c_int, (C.c_void_p, _PP, _PR, _PR, _PT, _PE, *_ERR)),
     "b200q_select_path": (C.c_int, (C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _PP, *_ERR)),
     "b200q_linear_forward": (C.c_int, (C.c_void_p, _PT, _PR, _PR, _PT, _PE, *_ERR)),
+    "b200q_linear_layer_create": (C.c_int, (C.c_void_p, _PT, C.c_int32, _PT, C.POINTER(C.c_void_p), *_ERR)),
+    "b200q_linear_layer_destroy": (None, (C.c_void_p,)),
+    "b200q_linear_layer_prepare": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, *_ERR)),
+    "b200q_linear_layer_forward": (C.c_int, (C.c_void_p, C.c_void_p, _PT, _PT, _PE, _PR, *_ERR)),
+    "b200q_linear_layer_weight": (C.c_int, (C.c_void_p, _PR, *_ERR)),
     "b200q_status": (C.c_int, (C.c_void_p, C.POINTER(C.c_int32), *_ERR)),
     "b200q_multiprocessors": (C.c_int, (C.c_void_p,)),
     "b200q_row_capacity": (C.c_int32, (C.c_int32, C.c_uint32)),

@@ -4,6 +4,8 @@
 #include "kernels/quant_dispatch.h"
 #include "ops/context.h"
 #include "ops/ops.h"
+#include "layers/linear.h"
+#include <vector>
 #include <cstdio>
 #include <cstring>
 #include <exception>
@@ -11,6 +13,11 @@
 
 struct b200q_context {
     std::unique_ptr<tts::CudaContext> gpu;
+};
+struct b200q_linear_layer {
+    std::unique_ptr<tts::Linear> layer;
+    std::unique_ptr<tts::QuantizationWorkspace> scratch;
+    int max_rows = 0;
 };
 
 namespace {
@@ -181,6 +188,50 @@ int b200q_linear_forward(b200q_context *c, const b200q_tensor *input, const b200
         TensorView bias = e.bias;
         e.bias = {};
         ops::linear(view_of(input), scaled_of(weight), bias, view_of(output), e, scaled_of(scratch));
+    });
+}
+int b200q_linear_layer_create(b200q_context *c, const b200q_tensor *parts, int32_t part_count, const b200q_tensor *bias,
+                              b200q_linear_layer **out, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        auto &gpu = context_of(c);
+        ExecutionScope scope(gpu);
+        if (!out || !parts || part_count < 1) throw std::invalid_argument("invalid layer arguments");
+        std::vector<TensorView> views;
+        for (int i = 0; i < part_count; ++i) views.push_back(view_of(parts + i));
+        auto holder = std::make_unique<b200q_linear_layer>();
+        holder->layer = std::make_unique<Linear>(Linear::quantize(views, gpu.mode, view_of(bias)));
+        *out = holder.release();
+    });
+}
+void b200q_linear_layer_destroy(b200q_linear_layer *l) { delete l; }
+int b200q_linear_layer_prepare(b200q_context *c, b200q_linear_layer *l, int32_t max_rows, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        ExecutionScope scope(context_of(c));
+        if (!l || !l->layer) throw std::invalid_argument("null layer");
+        l->layer->prepare_range(max_rows);
+        l->scratch = std::make_unique<QuantizationWorkspace>(max_rows, l->layer->workspace_capacity());
+        l->max_rows = max_rows;
+    });
+}
+int b200q_linear_layer_forward(b200q_context *c, b200q_linear_layer *l, const b200q_tensor *input, const b200q_tensor *output,
+                               const b200q_epilogue *epilogue, const b200q_row_scaled *quantized_output, char *error,
+                               size_t capacity) {
+    return guarded(error, capacity, [&] {
+        ExecutionScope scope(context_of(c));
+        if (!l || !l->layer) throw std::invalid_argument("null layer");
+        if (!l->scratch) throw std::logic_error("layer was not prepared before execution");
+        ops::Epilogue e = epilogue_of(epilogue);
+        if (e.bias.data) throw std::invalid_argument("linear already owns its bias");
+        l->layer->forward(*l->scratch, view_of(input), view_of(output), e,
+                          quantized_output ? scaled_of(quantized_output) : RowScaledView{});
+    });
+}
+int b200q_linear_layer_weight(b200q_linear_layer *l, b200q_row_scaled *weight, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        if (!l || !l->layer || !weight) throw std::invalid_argument("null layer");
+        auto w = l->layer->weight();
+        auto put = [](const TensorView &v) { return b200q_tensor{v.data, v.rows, v.cols, v.stride, int32_t(v.type), v.device}; };
+        *weight = {put(w.values), put(w.scales), w.group_size, w.rotation_size};
     });
 }
 int b200q_status(b200q_context *c, int32_t *status, char *error, size_t capacity) {

@@ -70,6 +70,14 @@ template <class T> __device__ __forceinline__ void load8(const T *p, int remaini
     }
 }
 
+// Register form of eight 16-bit elements and its conversion; lets a kernel issue all of its
+// 128-bit loads back to back before the first conversion waits on one of them.
+template <class T> __device__ __forceinline__ void unpack8(uint4 raw, float (&v)[8]) {
+    const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = float(e[i]);
+}
+
 template <Type F> __device__ __forceinline__ void store8(unsigned char *q, int remaining, bool aligned,
                                                         const float (&v)[8], float inverse) {
     uint32_t lo = Codec<F>::four(__fmul_rn(v[0], inverse), __fmul_rn(v[1], inverse),
@@ -161,10 +169,10 @@ __device__ __forceinline__ void quantize_tail(float (&v)[Items][8], unsigned cha
     if (!group) {
         float step = quant_scale<F>(cta_max<Threads>(amax, slots));
         float inverse = __fdiv_rn(1.f, step);
-        if (!threadIdx.x) scales[row] = step;
+        if (!threadIdx.x && !shard) scales[row] = step;
 #pragma unroll
         for (int j = 0; j < Items; ++j) {
-            int column = (j * Threads + int(threadIdx.x)) * 8;
+            int column = ((j * parts + shard) * Threads + int(threadIdx.x)) * 8;
             if (column < cols)
                 store8<F>(out + size_t(row) * cols + column, cols - column, aligned, v[j], inverse);
         }

@@ -84,11 +84,10 @@ Shape shape_for(int bn, bool grouped, int kb_per_split, int splits) {
     const size_t fixed = 1024 + reduce + scales;
     if (fixed + std::max(2 * stage, transposed) > kSmemBudget)
         throw std::invalid_argument("quantized GEMM: this tile/split combination exceeds shared memory; use more splits");
-    // Weight-streaming shapes (token tiles up to 64) take at most half an SM's shared memory, so two
-    // CTAs fit per SM: the next GEMM of the stream can already be resident and prefetching its weights
-    // while this one drains, and a tile's fixed latencies overlap another tile's streaming.
-    const size_t budget = (!grouped && bn <= 64) ? std::max(kSmemCompact, fixed + std::max(2 * stage, transposed)) : kSmemBudget;
-    int stages = int((budget - fixed) / stage);
+    // As many stages as fit (capped by the K blocks of one CTA): the ring is what gets prefetched
+    // while the upstream kernel is still running. Measured on the decode chain, deep rings with one
+    // CTA per SM beat half-size rings with two co-resident CTAs.
+    int stages = int((kSmemBudget - fixed) / stage);
     stages = std::max(2, std::min({stages, kMaxStages, std::max(2, kb_per_split)}));
 #ifdef B200Q_TIMING
     if (const char *forced = std::getenv("B200Q_STAGES")) stages = std::max(2, std::min(stages, std::atoi(forced)));
@@ -216,7 +215,7 @@ LinearPath select_tcgen05_path(KernelProblem p, Type format, int sms, size_t wor
         } catch (const std::invalid_argument &) {
             continue;
         }
-        const int per_sm = shape.smem <= kSmemCompact + 2048 ? 2 : 1;
+        const int per_sm = shape.smem <= kSmemCompact ? 2 : 1;
         const int64_t ctas = tiles * splits;
         const int64_t slots = int64_t(sms) * per_sm / splits * splits; // whole clusters only
         const double waves = double((ctas + slots - 1) / slots);
@@ -228,6 +227,14 @@ LinearPath select_tcgen05_path(KernelProblem p, Type format, int sms, size_t wor
             best = LinearPath{LinearKind::Tcgen05, bn, kBlockChannels, splits};
         }
     }
+#ifdef B200Q_TIMING
+    // experiment knob: "K:N=S,..." e.g. "2048:4096=4,6144:2048=3"
+    if (const char *forced = std::getenv("B200Q_SPLITS")) {
+        std::string text(forced), key = std::to_string(p.reduction) + ":" + std::to_string(p.channels) + "=";
+        auto at = text.find(key);
+        if (at != std::string::npos) best.splits = std::atoi(text.c_str() + at + key.size());
+    }
+#endif
     return best;
 }
 

@@ -59,9 +59,17 @@ struct FusedEpilogue {
 };
 
 #ifdef B200Q_TIMING
-#define B200Q_STAMP(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { long long t_; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_) :: "memory"); reinterpret_cast<long long *>(a.status + 16)[slot] = t_; } } while (0)
+// Debug build only: CTA 0 keeps (event -> global nanosecond timer) in shared memory and appends the
+// records to a log 64 KiB into the workspace when it exits; word 0 of the log is the record count.
+#define B200Q_STAMP(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { \
+    unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) :: "memory"); stamp_log[slot] = t_; } } while (0)
+#define B200Q_STAMP_FLUSH() do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { \
+    unsigned long long *log_ = reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(a.status) - kStatusOffset + 65536); \
+    unsigned long long at_ = atomicAdd(log_, 12ull); \
+    if (at_ < 60000) for (int s_ = 0; s_ < 12; ++s_) { log_[1 + 2 * (at_ + s_)] = (unsigned long long)(a.n) << 32 | (unsigned long long)(s_); log_[2 + 2 * (at_ + s_)] = stamp_log[s_]; } } } while (0)
 #else
 #define B200Q_STAMP(slot) do { } while (0)
+#define B200Q_STAMP_FLUSH() do { } while (0)
 #endif
 
 struct GemmArgs {
@@ -142,6 +150,11 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ float sx_tile[BN]; // per-row activation scales of this token tile
+#ifdef B200Q_TIMING
+    __shared__ unsigned long long stamp_log[12];
+    if (threadIdx.x < 12) stamp_log[threadIdx.x] = 0;
+    __syncthreads();
+#endif
 
     // Dynamic shared memory, 1024-byte aligned for the swizzled TMA boxes:
     //   [pipeline stages | split-K slots pushed by the cluster peers | K-group scales]
@@ -172,6 +185,7 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
             ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
         }
+
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(ptx::smem_u32(&acc_full[b]), 1);
             ptx::mbar_init(ptx::smem_u32(&acc_empty[b]), kEpilogueThreads / 32);
@@ -205,6 +219,7 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 ptx::tma_load_2d(tiles_base + uint32_t(i) * kStageBytes, &map_w, bar, (kb_begin + i) * kBlockK, n0);
             }
             ptx::wait_for_upstream();
+            B200Q_STAMP(9);
             for (int i = 0; i < ahead; ++i)
                 ptx::tma_load_2d(tiles_base + uint32_t(i) * kStageBytes + kWeightBytes, &map_x,
                                  ptx::smem_u32(&full_bar[i]), (kb_begin + i) * kBlockK, m0);
@@ -320,13 +335,17 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             ptx::tcgen05_fence_after();
             if (splits > 1) ptx::cluster_wait(); // every peer is running: its shared memory may be written
             if (ok) {
+                // Two chunks per round: both loads are in flight before the single wait.
 #pragma unroll 1
-                for (int chunk = half; chunk < kChunks; chunk += 2) {
+                for (int chunk = half; chunk < kChunks; chunk += 4) {
                     if (chunk * 16 >= valid_tokens) break;
-                    uint32_t r[16];
-                    ptx::tmem_load16(lane_base + uint32_t(chunk * 16), r);
+                    const bool second = chunk + 2 < kChunks && (chunk + 2) * 16 < valid_tokens;
+                    uint32_t r0[16], r1[16];
+                    ptx::tmem_load16(lane_base + uint32_t(chunk * 16), r0);
+                    if (second) ptx::tmem_load16(lane_base + uint32_t((chunk + 2) * 16), r1);
                     ptx::tmem_load_wait();
-                    emit_chunk(chunk, r);
+                    emit_chunk(chunk, r0);
+                    if (second) emit_chunk(chunk + 2, r1);
                 }
             }
         } else {
@@ -405,7 +424,64 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         if (e_thread == 0) B200Q_STAMP(8);
 
         // ---- phase 2: finish token rows; every global access is a 16-byte vector on a 256-byte row.
-        if (ok && !*abort_ptr && columns_ok) {
+        // The common case (bf16 out, aligned rows, nothing but an optional fp32 residual) takes a lean
+        // loop; everything else takes the general loop below it.
+        const bool lean = type == int(Type::BF16) && a.vector_io && !e.chain;
+        if (ok && !*abort_ptr && columns_ok && lean) {
+            const float *residual = e.residual_f32;
+            const size_t slot_stride = size_t(a.owned_passes) * kPassBytes;
+#pragma unroll 2
+            for (int local_pass = 0;; ++local_pass) {
+                const int pass = local_pass * splits + split;
+                if (pass >= passes) break;
+                const int c = pass * kRowsPerPass + row_in_pass;
+                if (c >= valid_tokens) continue;
+                const size_t at = size_t(m0 + c) * a.n + n;
+                float r8[8];
+                if (residual && local_pass > 0) {
+                    const float4 lo = *reinterpret_cast<const float4 *>(residual + at), hi = *reinterpret_cast<const float4 *>(residual + at + 4);
+                    r8[0] = lo.x; r8[1] = lo.y; r8[2] = lo.z; r8[3] = lo.w; r8[4] = hi.x; r8[5] = hi.y; r8[6] = hi.z; r8[7] = hi.w;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) r8[i] = first_residual[i];
+                }
+                uint32_t raw[8];
+                if (splits == 1) {
+                    const uint8_t *src = tiles_ptr + size_t(c * kBlockChannels + 8 * j) * 4;
+                    const uint4 lo = *reinterpret_cast<const uint4 *>(src), hi = *reinterpret_cast<const uint4 *>(src + 16);
+                    raw[0] = lo.x; raw[1] = lo.y; raw[2] = lo.z; raw[3] = lo.w; raw[4] = hi.x; raw[5] = hi.y; raw[6] = hi.z; raw[7] = hi.w;
+                } else {
+                    const uint8_t *src = reduce_ptr + size_t(local_pass) * kPassBytes + size_t(row_in_pass * kBlockChannels + 8 * j) * 4;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) raw[i] = 0u;
+                    for (int s = 0; s < splits; ++s) {
+                        const uint4 lo = *reinterpret_cast<const uint4 *>(src + s * slot_stride);
+                        const uint4 hi = *reinterpret_cast<const uint4 *>(src + s * slot_stride + 16);
+                        const uint32_t part[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            raw[i] = kIntAcc ? uint32_t(int(raw[i]) + int(part[i]))
+                                             : __float_as_uint(__fadd_rn(__uint_as_float(raw[i]), __uint_as_float(part[i])));
+                    }
+                }
+                const float scale_x = sx_tile[Grouped ? 0 : c];
+                float value[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float acc = kIntAcc ? float(int(raw[i])) : __uint_as_float(raw[i]);
+                    value[i] = Grouped ? acc : __fmul_rn(__fmul_rn(acc, scale_x), sw8[i]);
+                    if (residual) value[i] = __fadd_rn(value[i], r8[i]);
+                }
+                uint4 packed;
+                {
+                    __nv_bfloat162 b0 = __floats2bfloat162_rn(value[0], value[1]), b1 = __floats2bfloat162_rn(value[2], value[3]);
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(value[4], value[5]), b3 = __floats2bfloat162_rn(value[6], value[7]);
+                    packed = make_uint4(*reinterpret_cast<uint32_t *>(&b0), *reinterpret_cast<uint32_t *>(&b1),
+                                        *reinterpret_cast<uint32_t *>(&b2), *reinterpret_cast<uint32_t *>(&b3));
+                }
+                *reinterpret_cast<uint4 *>(static_cast<uint16_t *>(a.out) + at) = packed;
+            }
+        } else if (ok && !*abort_ptr && columns_ok) {
             for (int local_pass = 0;; ++local_pass) {
                 const int pass = local_pass * splits + split;
                 if (pass >= passes) break;
@@ -495,7 +571,15 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     if (warp < 2 && splits > 1) ptx::cluster_sync(); // the producer/MMA warps' share of the phase barrier
 
     __syncthreads(); // tensor memory is drained and nobody else will touch this CTA's shared memory
-    if (threadIdx.x == 0) B200Q_STAMP(6);
+    if (threadIdx.x == 0) { B200Q_STAMP(6); B200Q_STAMP_FLUSH(); }
+#ifdef B200Q_TIMING
+    if (threadIdx.x == 0) { // every CTA: its own end time (event 20)
+        unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) :: "memory");
+        unsigned long long *log_ = reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(a.status) - kStatusOffset + 65536);
+        unsigned long long at_ = atomicAdd(log_, 1ull);
+        if (at_ < 60000) { log_[1 + 2 * at_] = (unsigned long long)(a.n) << 32 | 20ull; log_[2 + 2 * at_] = t_; }
+    }
+#endif
     if (warp == 1) {
         ptx::tcgen05_fence_after();
         ptx::tmem_dealloc(tmem_base, kTmemColumns);

@@ -27,14 +27,26 @@ row_quantize_cached(const T *__restrict__ x, unsigned char *__restrict__ q, floa
     const int row = blockIdx.x / parts, shard = blockIdx.x % parts;
     const T *source = x + size_t(row) * stride;
     float v[Items][8];
+    if (aligned) {
+        // All loads of the row shard are issued before the first value is used.
+        uint4 raw[Items];
 #pragma unroll
-    for (int j = 0; j < Items; ++j) {
-        int column = ((j * parts + shard) * kThreads + int(threadIdx.x)) * 8;
-        if (column < cols) {
-            load8(source + column, cols - column, aligned, v[j]);
-        } else {
+        for (int j = 0; j < Items; ++j) {
+            int column = ((j * parts + shard) * kThreads + int(threadIdx.x)) * 8;
+            raw[j] = column < cols ? *reinterpret_cast<const uint4 *>(source + column) : make_uint4(0, 0, 0, 0);
+        }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
+        for (int j = 0; j < Items; ++j) unpack8<T>(raw[j], v[j]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < Items; ++j) {
+            int column = ((j * parts + shard) * kThreads + int(threadIdx.x)) * 8;
+            if (column < cols) {
+                load8(source + column, cols - column, false, v[j]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
+            }
         }
     }
     quantize_tail<F, kThreads, Items, Rotate>(v, q, scales, row, rows, cols, group, shard, parts,

@@ -159,3 +159,45 @@ class Context:
         value = C.c_int32(0)
         _lib.call("b200q_status", self._handle, C.byref(value))
         return value.value
+
+
+class Linear:
+    """Quantized Linear layer (reference: tts::Linear, src/layers/linear.h:11-76): fuses the given 16-bit
+    weight matrices by rows, quantizes them on the device at construction (the load-time step of
+    Weights::quantized), and runs quantize -> GEMM -> fused epilogue per call."""
+
+    def __init__(self, ctx: Context, parts: list[torch.Tensor], bias: torch.Tensor | None = None, max_rows: int = 64):
+        self.ctx = ctx
+        self._keep = (parts, bias)
+        array = (Tensor * len(parts))(*[_tensor(p) for p in parts])
+        handle = C.c_void_p()
+        _lib.call("b200q_linear_layer_create", ctx._handle, array, len(parts), C.byref(_tensor(bias)), C.byref(handle))
+        self._handle = handle
+        self.out_features = sum(p.shape[0] for p in parts)
+        self.in_features = parts[0].shape[1]
+        _lib.call("b200q_linear_layer_prepare", ctx._handle, self._handle, max_rows)
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None, quantized_output: RowScaledView | None = None,
+                **epilogue) -> torch.Tensor:
+        if out is None:
+            out = torch.empty(x.shape[0], self.out_features, dtype=x.dtype, device=x.device)
+        ep = C.byref(_epilogue(**epilogue)) if epilogue else None
+        qo = C.byref(quantized_output.c()) if quantized_output is not None else None
+        _lib.call("b200q_linear_layer_forward", self.ctx._handle, self._handle, C.byref(_tensor(x)), C.byref(_tensor(out)), ep, qo)
+        return out
+
+    def weight(self) -> RowScaled:
+        view = RowScaled()
+        _lib.call("b200q_linear_layer_weight", self._handle, C.byref(view))
+        return view
+
+    def close(self):
+        if getattr(self, "_handle", None):
+            _lib.load().b200q_linear_layer_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -109,6 +109,26 @@ int b200q_linear_forward(b200q_context *, const b200q_tensor *input, const b200q
                          const b200q_row_scaled *scratch, const b200q_tensor *output,
                          const b200q_epilogue *epilogue, char *error, size_t error_capacity);
 
+/* ---- Linear layer object --------------------------------------------------------------------
+ * reference: tts::Linear (src/layers/linear.h:11-76) over a quantized weight, with the load-time
+ * step of Weights::quantized (src/io/weights.cpp:80-87,133-154): `parts` are `part_count` 16-bit
+ * [N_i, K] matrices fused by rows (Q,K,V -> QKV; gate,up -> gate_up) and quantized on the device
+ * into storage the layer owns, in the context's mode. bias may be NULL or have data == NULL. */
+typedef struct b200q_linear_layer b200q_linear_layer;
+int b200q_linear_layer_create(b200q_context *, const b200q_tensor *parts, int32_t part_count, const b200q_tensor *bias,
+                              b200q_linear_layer **out, char *error, size_t error_capacity);
+void b200q_linear_layer_destroy(b200q_linear_layer *);
+/* reference: Linear::prepare_range (src/layers/linear.cpp:132-148): plans for every row class up to
+ * max_rows, and the layer's activation scratch (QuantizationWorkspace) sized for max_rows. */
+int b200q_linear_layer_prepare(b200q_context *, b200q_linear_layer *, int32_t max_rows, char *error, size_t error_capacity);
+/* reference: Linear::forward(workspace, input, output, epilogue, quantized_output)
+ * (src/layers/linear.h:66-68). quantized_output may be NULL. */
+int b200q_linear_layer_forward(b200q_context *, b200q_linear_layer *, const b200q_tensor *input, const b200q_tensor *output,
+                               const b200q_epilogue *epilogue, const b200q_row_scaled *quantized_output, char *error,
+                               size_t error_capacity);
+/* The layer's quantized weight view (borrowed; valid while the layer lives). */
+int b200q_linear_layer_weight(b200q_linear_layer *, b200q_row_scaled *weight, char *error, size_t error_capacity);
+
 /* Blocks until the context's stream is idle and returns the device status word through `status`:
  * 0 = clean; nonzero = a bounded device-side wait gave up (results are invalid). */
 int b200q_status(b200q_context *, int32_t *status, char *error, size_t error_capacity);
