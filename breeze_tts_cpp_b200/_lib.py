@@ -56,6 +56,7 @@ SIGNATURES = {
     "b200q_linear_layer_prepare": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, *_ERR)),
     "b200q_linear_layer_forward": (C.c_int, (C.c_void_p, C.c_void_p, _PT, _PT, _PE, _PR, *_ERR)),
     "b200q_linear_layer_weight": (C.c_int, (C.c_void_p, _PR, *_ERR)),
+    "b200q_quant_linear_static": (C.c_int, (C.c_int32, C.c_void_p, _PP, _PR, _PR, _PT, _PE, *_ERR)),
     "b200q_status": (C.c_int, (C.c_void_p, C.POINTER(C.c_int32), *_ERR)),
     "b200q_multiprocessors": (C.c_int, (C.c_void_p,)),
     "b200q_row_capacity": (C.c_int32, (C.c_int32, C.c_uint32)),

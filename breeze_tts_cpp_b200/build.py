@@ -26,6 +26,7 @@ SOURCES = [
     ("kernels/quant_norm.cu", ["--fmad=false"]),
     ("kernels/quant_gated.cu", ["--fmad=false"]),
     ("kernels/quant_linear.cu", []),
+    ("kernels/quant_linear_static.cu", []),
     ("ops/quantized_gemm.cpp", []),
     ("ops/context.cpp", []),
     ("ops/ops.cpp", []),

@@ -129,6 +129,18 @@ int b200q_linear_layer_forward(b200q_context *, b200q_linear_layer *, const b200
 /* The layer's quantized weight view (borrowed; valid while the layer lives). */
 int b200q_linear_layer_weight(b200q_linear_layer *, b200q_row_scaled *weight, char *error, size_t error_capacity);
 
+/* No counterpart in the reference. The same GEMM as b200q_quant_linear for callers that cannot
+ * allocate device memory (an engine whose pools are sealed, a region where cudaMalloc is not
+ * allowed, a host that provides a stream but no workspace): needs no context and no workspace, its
+ * 32 KiB of scratch is a device array built into the library. `path` NULL lets the planner choose.
+ * Limits: one array per GPU shared by every call, so calls that overlap on the GPU race and each call
+ * finds the previous call's contents (the status word is cleared per call); problems needing more
+ * than 32 KiB of scratch are rejected; the first call on a device does one-time set-up and should
+ * come before any stream capture. */
+int b200q_quant_linear_static(int32_t device, void *stream, const b200q_path *path, const b200q_row_scaled *input,
+                              const b200q_row_scaled *weight, const b200q_tensor *output,
+                              const b200q_epilogue *epilogue, char *error, size_t error_capacity);
+
 /* Blocks until the context's stream is idle and returns the device status word through `status`:
  * 0 = clean; nonzero = a bounded device-side wait gave up (results are invalid). */
 int b200q_status(b200q_context *, int32_t *status, char *error, size_t error_capacity);
