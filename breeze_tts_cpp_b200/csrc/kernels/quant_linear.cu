@@ -3,6 +3,7 @@
 // (src/ops/kernels/quant/quant_dispatch.cu:194-234, quant_grouped.cu:221-239).
 #include "kernels/quant_dispatch.h"
 #include "kernels/quant_linear_sm100.cuh"
+#include "kernels/quant_prefill_sm100.cuh"
 #include "ops/epilogue.h"
 #include <cuda.h>
 #include <cstdlib>
@@ -143,7 +144,35 @@ template <Type F, bool Grouped, int BN> void raise_limit() {
                                int(kSmemBudget)),
           "cudaFuncSetAttribute(shared memory)");
 }
+constexpr size_t kPrefillSmem = 1024 + size_t(kPrefillStages) * (kBlockChannels + kPrefillTokens) * kBlockK;
+int multiprocessor_count() {
+    static int cached[64] = {};
+    int device = 0;
+    check(cudaGetDevice(&device), "cudaGetDevice");
+    if (device < 0 || device >= 64) return 148;
+    if (!cached[device])
+        check(cudaDeviceGetAttribute(&cached[device], cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute");
+    return cached[device];
+}
+template <Type F>
+void launch_prefill(const CUtensorMap &map_w, const CUtensorMap &map_x, const PrefillArgs &args, cudaStream_t stream) {
+    const int tiles = ((args.n + kBlockChannels - 1) / kBlockChannels) * ((args.m + kPrefillTokens - 1) / kPrefillTokens);
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(unsigned(std::min(tiles, multiprocessor_count())));
+    config.blockDim = dim3(kGemmThreads);
+    config.dynamicSmemBytes = kPrefillSmem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    check(cudaLaunchKernelEx(&config, w8a8_tcgen05_prefill<F>, map_w, map_x, args), "quantized prefill GEMM launch");
+}
+
 template <Type F> void raise_limits() {
+    check(cudaFuncSetAttribute(w8a8_tcgen05_prefill<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kPrefillSmem)),
+          "cudaFuncSetAttribute(shared memory)");
     raise_limit<F, false, 16>(); raise_limit<F, false, 32>(); raise_limit<F, false, 64>();
     raise_limit<F, false, 128>(); raise_limit<F, false, 256>();
     raise_limit<F, true, 16>(); raise_limit<F, true, 32>(); raise_limit<F, true, 64>(); raise_limit<F, true, 128>();
@@ -293,12 +322,19 @@ void launch_quant_linear(LinearPath config, KernelProblem shape, const void *inp
         vector_io = vector_io && aligned16(e.residual_f32.data);
     }
     args.vector_io = vector_io;
+    const CUtensorMap &map_w = tensor_map(weights, shape.channels, shape.reduction, kBlockChannels, true);
+    const CUtensorMap &map_x = tensor_map(input, shape.rows, shape.reduction, bn, false);
+    // Compute-bound shapes with a plain epilogue take the persistent, double-buffered kernel.
+    if (!grouped && bn == kPrefillTokens && splits == 1 && !args.ep.chain && output_type != Type::I32) {
+        PrefillArgs prefill{args.m, args.n, args.k, xs, ws, y, int(output_type), args.ep.residual_f32, args.status};
+        if (format == Type::I8) launch_prefill<Type::I8>(map_w, map_x, prefill, stream);
+        else launch_prefill<Type::FP8>(map_w, map_x, prefill, stream);
+        return;
+    }
     const Shape launch = shape_for(bn, grouped, (kb_total + splits - 1) / splits, splits);
     args.stages = launch.stages;
     args.tile_region = int(launch.tile_region);
     args.owned_passes = launch.owned_passes;
-    const CUtensorMap &map_w = tensor_map(weights, shape.channels, shape.reduction, kBlockChannels, true);
-    const CUtensorMap &map_x = tensor_map(input, shape.rows, shape.reduction, bn, false);
     dim3 grid(n_tiles, m_tiles, splits);
     if (format == Type::I8) {
         if (grouped) launch_tokens<Type::I8, true>(bn, map_w, map_x, args, grid, launch.smem, stream);

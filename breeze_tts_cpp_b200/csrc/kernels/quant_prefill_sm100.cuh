@@ -1,0 +1,185 @@
+// Compute-bound (prefill) variant of the W8A8 GEMM for sm_100a: persistent CTAs, 128-channel x
+// 256-token tiles, two accumulators in tensor memory so that the dequant epilogue of tile i runs
+// while the tensor cores work on tile i+1.
+//
+// Same orientation and arithmetic as the weight-streaming kernel (quant_linear_sm100.cuh): 128
+// weight channels are the MMA M rows, 256 tokens the MMA N columns, K in 128-byte swizzled TMA
+// boxes; out[m,n] = D((float(acc) * sx[m]) * sw[n]) (+ fp32 residual), per-row scales only.
+// Replaces the reference's compute-bound paths: CUTLASS SM80 `Sm80Gemm`
+// (src/ops/kernels/quant/quant_gemm_sm80.cu:14-82) and the SM90a WGMMA family
+// (quant_gemm_sm90.cu:16-69), neither of which uses Blackwell's tensor memory.
+//
+// Roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer and tensor-memory owner,
+// warps 2-9 = epilogue (two warps per 32-lane quadrant, alternating 16-token chunks).
+// Tiles are dealt round-robin: tile = blockIdx.x + i * gridDim.x, channel tile fastest, so the CTAs
+// running at any moment share a few activation row blocks and the whole weight matrix through L2.
+#pragma once
+#include "kernels/quant_linear_sm100.cuh"
+
+namespace tts::b200 {
+
+constexpr int kPrefillTokens = 256;
+constexpr int kPrefillStages = 4;
+
+struct PrefillArgs {
+    int m, n, k;
+    const float *sx, *sw;
+    void *out;
+    int out_type; // Type::BF16 or Type::F16
+    const float *residual_f32;
+    int *status;
+};
+
+template <Type F>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+w8a8_tcgen05_prefill(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                     const PrefillArgs a) {
+    constexpr bool kInt = F == Type::I8;
+    constexpr int BN = kPrefillTokens;
+    constexpr int kWeightBytes = kBlockChannels * kBlockK, kTokenBytes = BN * kBlockK;
+    constexpr int kStageBytes = kWeightBytes + kTokenBytes;
+    constexpr uint32_t kIdesc = kInt ? ptx::idesc_i8(kBlockChannels, BN) : ptx::idesc_e4m3(kBlockChannels, BN);
+
+    extern __shared__ uint8_t dynamic_smem[];
+    __shared__ alignas(8) uint64_t full_bar[kPrefillStages], empty_bar[kPrefillStages], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    __shared__ float sx_tile[2][BN]; // activation scales of the tile in each accumulator
+
+    const uint32_t raw_base = ptx::smem_u32(dynamic_smem);
+    const uint32_t tiles_base = (raw_base + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tiles = (a.n + kBlockChannels - 1) / kBlockChannels, m_tiles = (a.m + BN - 1) / BN;
+    const int tiles = n_tiles * m_tiles;
+    const int kb_count = (a.k + kBlockK - 1) / kBlockK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPrefillStages; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&acc_full[b]), 1);
+            ptx::mbar_init(ptx::smem_u32(&acc_empty[b]), kEpilogueThreads / 32);
+        }
+        abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+    }
+    if (warp == 1) ptx::tmem_alloc(ptx::smem_u32(&tmem_slot), 512);
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    ptx::tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    volatile int *abort_ptr = &abort_flag;
+    ptx::launch_dependents();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&map_w);
+            ptx::prefetch_tensormap(&map_x);
+            ptx::wait_for_upstream();
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const int n0 = (tile % n_tiles) * kBlockChannels, m0 = (tile / n_tiles) * BN;
+                for (int kb = 0; kb < kb_count; ++kb) {
+                    if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_ptr)) { ok = false; break; }
+                    const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
+                    const uint32_t dst = tiles_base + uint32_t(stage) * kStageBytes;
+                    ptx::mbar_arrive_expect_tx(bar, kStageBytes);
+                    ptx::tma_load_2d(dst, &map_w, bar, kb * kBlockK, n0);
+                    ptx::tma_load_2d(dst + kWeightBytes, &map_x, bar, kb * kBlockK, m0);
+                    if (++stage == kPrefillStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int stage = 0, local = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+                const int buffer = local & 1;
+                // The epilogue must have drained this accumulator (two tiles ago).
+                if (!ptx::mbar_wait(ptx::smem_u32(&acc_empty[buffer]), ((uint32_t(local) >> 1) & 1u) ^ 1u, abort_ptr)) break;
+                ptx::tcgen05_fence_after();
+                const uint32_t d = tmem_base + uint32_t(buffer * BN);
+                for (int kb = 0; kb < kb_count; ++kb) {
+                    if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_ptr)) { ok = false; break; }
+                    ptx::tcgen05_fence_after();
+                    const uint32_t tile_smem = tiles_base + uint32_t(stage) * kStageBytes;
+                    const uint64_t desc_w = ptx::smem_desc_k128(tile_smem), desc_x = ptx::smem_desc_k128(tile_smem + kWeightBytes);
+#pragma unroll
+                    for (int step = 0; step < kBlockK / 32; ++step) {
+                        const uint32_t accumulate = (kb > 0 || step > 0);
+                        if (kInt) ptx::mma_i8(d, desc_w + uint64_t(step * 2), desc_x + uint64_t(step * 2), kIdesc, accumulate);
+                        else ptx::mma_f8(d, desc_w + uint64_t(step * 2), desc_x + uint64_t(step * 2), kIdesc, accumulate);
+                    }
+                    ptx::tcgen05_commit(ptx::smem_u32(&empty_bar[stage]));
+                    if (++stage == kPrefillStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) ptx::tcgen05_commit(ptx::smem_u32(&acc_full[buffer]));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps
+        const int e_thread = threadIdx.x - 64;
+        const int quadrant = warp & 3, half = (warp - 2) >> 2;
+        const int channel_in_tile = quadrant * 32 + lane;
+        const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16);
+        const bool bf16_out = a.out_type == int(Type::BF16);
+        ptx::wait_for_upstream();
+        int local = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+            const int buffer = local & 1;
+            const int n0 = (tile % n_tiles) * kBlockChannels, m0 = (tile / n_tiles) * BN;
+            const int valid_tokens = min(BN, a.m - m0);
+            const int n = n0 + channel_in_tile;
+            const bool channel_ok = n < a.n;
+            const float scale_w = channel_ok ? a.sw[n] : 0.f;
+            // Stage this tile's activation scales while the tensor cores are still busy with it.
+            sx_tile[buffer][e_thread] = e_thread < valid_tokens ? a.sx[m0 + e_thread] : 0.f;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (!ptx::mbar_wait(ptx::smem_u32(&acc_full[buffer]), (uint32_t(local) >> 1) & 1u, abort_ptr)) break;
+            ptx::tcgen05_fence_after();
+#pragma unroll 1
+            for (int chunk = half; chunk < BN / 16; chunk += 2) {
+                if (chunk * 16 >= valid_tokens) break;
+                uint32_t r[16];
+                ptx::tmem_load16(lane_base + uint32_t(buffer * BN + chunk * 16), r);
+                ptx::tmem_load_wait();
+                if (channel_ok) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int c = chunk * 16 + i;
+                        if (c < valid_tokens) {
+                            const size_t at = size_t(m0 + c) * a.n + n;
+                            const float acc = kInt ? float(int(r[i])) : __uint_as_float(r[i]);
+                            float value = __fmul_rn(__fmul_rn(acc, sx_tile[buffer][c]), scale_w);
+                            if (a.residual_f32) value = __fadd_rn(value, a.residual_f32[at]);
+                            if (bf16_out) static_cast<__nv_bfloat16 *>(a.out)[at] = __float2bfloat16_rn(value);
+                            else static_cast<__half *>(a.out)[at] = __float2half_rn(value);
+                        }
+                    }
+                }
+            }
+            // This warp has read everything it needs from the accumulator: hand it back.
+            ptx::tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&acc_empty[buffer]));
+        }
+        ptx::tcgen05_fence_before();
+    }
+
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tcgen05_fence_after();
+        ptx::tmem_dealloc(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 && abort_flag) atomicExch(a.status, 1 + int(blockIdx.x));
+}
+} // namespace tts::b200
