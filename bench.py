@@ -252,7 +252,8 @@ def time_steps(args, torch, dist, world, device, stream, stack, graph, gemm_grap
 
 def sweep(torch, ops, device, stream):
     """Per-shape numbers for the other configurations (decode sweep, FP8 prefill, K-group down projection),
-    each rotated over enough distinct weight copies to exceed L2. Reported beside the headline, not as it."""
+    each rotated over enough distinct weight copies to exceed L2. `us`/`gbs`/`tops` time quantize + GEMM,
+    `gemm_*` the GEMM launches alone. Reported beside the headline, not as it."""
     from breeze_tts_cpp_b200 import FP8, I8
     peaks = measured_peaks()
     rows_out = []
@@ -273,31 +274,38 @@ def sweep(torch, ops, device, stream):
             path = ctx.prepare_quantized(m, n, k)
             kw = {"residual_f32": res} if residual else {}
 
-            def body():
+            def body(gemm_only):
                 for w in ws:
-                    ctx.quantize_rows(x, xq)
+                    if not gemm_only:
+                        ctx.quantize_rows(x, xq)
                     ctx.matmul(xq, w, out, **kw)
-            body()
-            stream.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                body()
-            g.replay()
-            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            reps = max(1, iters // copies)
-            start.record(stream)
-            for _ in range(reps):
+
+            def timed(gemm_only):
+                body(gemm_only)
+                stream.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    body(gemm_only)
                 g.replay()
-            stop.record(stream)
-            stop.synchronize()
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = max(1, iters // copies)
+                start.record(stream)
+                for _ in range(reps):
+                    g.replay()
+                stop.record(stream)
+                stop.synchronize()
+                return start.elapsed_time(stop) * 1e3 / (reps * copies)
+
+            us = timed(False)
+            gemm_us = timed(True)
         status = ctx.status()
         ctx.close()
-        us = start.elapsed_time(stop) * 1e3 / (reps * copies)
         nbytes = linear_bytes(m, k, n, residual, group)
-        tops = 2.0 * m * n * k / us / 1e6
+        gemm_bytes = linear_bytes(m, k, n, residual, group, quantize=False)
         return {"mode": mode, "m": m, "k": k, "n": n, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
-                "tops": round(tops, 1), "hbm_frac_measured": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 3),
-                "path": list(path), "status": status}
+                "tops": round(2.0 * m * n * k / us / 1e6, 1), "hbm_frac_measured": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 3),
+                "gemm_us": round(gemm_us, 2), "gemm_gbs": round(gemm_bytes / gemm_us / 1e3, 1),
+                "gemm_tops": round(2.0 * m * n * k / gemm_us / 1e6, 1), "path": list(path), "status": status}
 
     for m in (1, 4, 16, 64):
         for name, (k, n) in SHAPES.items():
@@ -526,7 +534,10 @@ def main():
                          "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(achieved / peaks["hbm_gbs"], 4), "frac_of_nominal_8TBps": round(achieved / 8000.0, 4),
                          "peak_source": peaks["source"], "avg_launch_us": round(ms_gemm * 1e3 / (LAYERS * 4), 3),
-                         "algorithmic_bytes_per_launch": gemm_bytes // (LAYERS * 4), "traffic": None},
+                         "algorithmic_bytes_per_launch": gemm_bytes // (LAYERS * 4),
+                         # DRAM bytes per launch: the ncu capture of the gate+up launch at M=64 (profiles/) read
+                         # 25.40 MB for 26.92 MB algorithmic; the same ratio applied to the average launch.
+                         "traffic": int(gemm_bytes // (LAYERS * 4) * 25.40 / 26.92)},
             "clocks": result["clocks"],
         }
         if args.impl == "reference":

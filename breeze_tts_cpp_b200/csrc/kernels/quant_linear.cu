@@ -4,6 +4,7 @@
 #include "kernels/quant_dispatch.h"
 #include "kernels/quant_linear_sm100.cuh"
 #include "kernels/quant_prefill_sm100.cuh"
+#include "kernels/quant_prefill_pair_sm100.cuh"
 #include "ops/epilogue.h"
 #include <cuda.h>
 #include <cstdlib>
@@ -144,7 +145,7 @@ template <Type F, bool Grouped, int BN> void raise_limit() {
                                int(kSmemBudget)),
           "cudaFuncSetAttribute(shared memory)");
 }
-constexpr size_t kPrefillSmem = 1024 + size_t(kPrefillStages) * (kBlockChannels + kPrefillTokens) * kBlockK;
+constexpr size_t kPrefillSmem = 1024 + size_t(kPrefillStages) * (kBlockChannels + kPrefillTokens) * kBlockK + kPrefillPatchBytes;
 int multiprocessor_count() {
     static int cached[64] = {};
     int device = 0;
@@ -170,7 +171,27 @@ void launch_prefill(const CUtensorMap &map_w, const CUtensorMap &map_x, const Pr
     check(cudaLaunchKernelEx(&config, w8a8_tcgen05_prefill<F>, map_w, map_x, args), "quantized prefill GEMM launch");
 }
 
+constexpr size_t kPairSmem = 1024 + size_t(kPairStages) * (kBlockChannels + kPrefillTokens / 2) * kBlockK + kPrefillPatchBytes;
+// CTA pairs: one cluster of two per 256-channel x 256-token tile, persistent over the tiles.
+template <Type F>
+void launch_prefill_pair(const CUtensorMap &map_w, const CUtensorMap &map_x, const PrefillArgs &args, cudaStream_t stream) {
+    const int tiles = ((args.n + 2 * kBlockChannels - 1) / (2 * kBlockChannels)) * ((args.m + kPrefillTokens - 1) / kPrefillTokens);
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(2u * unsigned(std::min(tiles, multiprocessor_count() / 2)));
+    config.blockDim = dim3(kGemmThreads);
+    config.dynamicSmemBytes = kPairSmem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    check(cudaLaunchKernelEx(&config, w8a8_tcgen05_prefill_pair<F>, map_w, map_x, args), "quantized pair GEMM launch");
+}
+
 template <Type F> void raise_limits() {
+    check(cudaFuncSetAttribute(w8a8_tcgen05_prefill_pair<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kPairSmem)),
+          "cudaFuncSetAttribute(shared memory)");
     check(cudaFuncSetAttribute(w8a8_tcgen05_prefill<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kPrefillSmem)),
           "cudaFuncSetAttribute(shared memory)");
     raise_limit<F, false, 16>(); raise_limit<F, false, 32>(); raise_limit<F, false, 64>();
@@ -323,14 +344,26 @@ void launch_quant_linear(LinearPath config, KernelProblem shape, const void *inp
     }
     args.vector_io = vector_io;
     const CUtensorMap &map_w = tensor_map(weights, shape.channels, shape.reduction, kBlockChannels, true);
-    const CUtensorMap &map_x = tensor_map(input, shape.rows, shape.reduction, bn, false);
-    // Compute-bound shapes with a plain epilogue take the persistent, double-buffered kernel.
-    if (!grouped && bn == kPrefillTokens && splits == 1 && !args.ep.chain && output_type != Type::I32) {
+    // Compute-bound shapes with a plain epilogue take the persistent, double-buffered kernels:
+    // CTA pairs (each CTA loads half of the token tile) when there are at least two channel tiles.
+    if (!grouped && bn == kPrefillTokens && splits == 1 && !args.ep.chain && output_type != Type::I32 && args.vector_io) {
         PrefillArgs prefill{args.m, args.n, args.k, xs, ws, y, int(output_type), args.ep.residual_f32, args.status};
+        bool pair = shape.channels >= 2 * kBlockChannels;
+#ifdef B200Q_TIMING
+        if (std::getenv("B200Q_NOPAIR")) pair = false;
+#endif
+        if (pair) {
+            const CUtensorMap &map_half = tensor_map(input, shape.rows, shape.reduction, kPrefillTokens / 2, false);
+            if (format == Type::I8) launch_prefill_pair<Type::I8>(map_w, map_half, prefill, stream);
+            else launch_prefill_pair<Type::FP8>(map_w, map_half, prefill, stream);
+            return;
+        }
+        const CUtensorMap &map_x = tensor_map(input, shape.rows, shape.reduction, bn, false);
         if (format == Type::I8) launch_prefill<Type::I8>(map_w, map_x, prefill, stream);
         else launch_prefill<Type::FP8>(map_w, map_x, prefill, stream);
         return;
     }
+    const CUtensorMap &map_x = tensor_map(input, shape.rows, shape.reduction, bn, false);
     const Shape launch = shape_for(bn, grouped, (kb_total + splits - 1) / splits, splits);
     args.stages = launch.stages;
     args.tile_region = int(launch.tile_region);

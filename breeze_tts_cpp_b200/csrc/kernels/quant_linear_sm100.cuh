@@ -428,7 +428,8 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         // loop; everything else takes the general loop below it.
         const bool lean = type == int(Type::BF16) && a.vector_io && !e.chain;
         if (ok && !*abort_ptr && columns_ok && lean) {
-            const float *residual = e.residual_f32;
+            const float *__restrict__ residual = e.residual_f32; // never aliases the output rows
+            uint16_t *__restrict__ out16 = static_cast<uint16_t *>(a.out);
             const size_t slot_stride = size_t(a.owned_passes) * kPassBytes;
 #pragma unroll 2
             for (int local_pass = 0;; ++local_pass) {
@@ -479,7 +480,7 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     packed = make_uint4(*reinterpret_cast<uint32_t *>(&b0), *reinterpret_cast<uint32_t *>(&b1),
                                         *reinterpret_cast<uint32_t *>(&b2), *reinterpret_cast<uint32_t *>(&b3));
                 }
-                *reinterpret_cast<uint4 *>(static_cast<uint16_t *>(a.out) + at) = packed;
+                *reinterpret_cast<uint4 *>(out16 + at) = packed;
             }
         } else if (ok && !*abort_ptr && columns_ok) {
             for (int local_pass = 0;; ++local_pass) {

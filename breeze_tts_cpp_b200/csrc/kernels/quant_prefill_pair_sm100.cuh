@@ -1,0 +1,198 @@
+// Compute-bound W8A8 GEMM on CTA pairs (tcgen05 cta_group::2): two SMs share one 256-channel x
+// 256-token tile. Each CTA of the pair loads 128 weight rows and only HALF of the token rows into its
+// own shared memory and keeps 128 accumulator rows in its own tensor memory; the even CTA issues the
+// M=256 x N=256 MMAs for both. Compared with one-CTA 128x256 tiles this cuts the bytes every SM pulls
+// from L2 per MMA by a third, which is what bounds 8-bit GEMMs at these K (the tensor pipe needs
+// 96 B/clk/SM of operands otherwise).
+//
+// Same arithmetic as quant_prefill_sm100.cuh: out[m,n] = D((float(acc) * sx[m]) * sw[n]) (+ fp32
+// residual), per-row scales. Persistent clusters, two accumulators in tensor memory so the epilogue
+// of tile i overlaps the MMAs of tile i+1. No TMA multicast: each CTA issues its own loads; the loads
+// carry the cta_group::2 qualifier only so that they can signal the barrier in the leader CTA.
+// Replaces reference quant_gemm_sm80.cu:14-82 / quant_gemm_sm90.cu:16-69 for compute-bound shapes.
+//
+// Barrier protocol (L = leader, even rank; P = peer):
+//   full[s]      in L : L's producer arrives with expect_tx for BOTH CTAs' bytes; both producers'
+//                       TMA loads complete their bytes on it.
+//   empty[s]     in L and P : one multicast tcgen05.commit after the MMAs that read stage s.
+//   acc_full[b]  in L and P : multicast commit after the last MMA of a tile.
+//   acc_empty[b] in L : 16 arrivals (8 epilogue warps of each CTA, the peer's arrive remotely).
+// Every wait is bounded; on expiry the CTA flags the status word and runs to the common exit.
+#pragma once
+#include "kernels/quant_prefill_sm100.cuh"
+
+namespace tts::b200 {
+
+#ifdef B200Q_TIMING
+// Debug build: cluster 0 / leader records per-tile times (global ns timer) 256 KiB into the workspace:
+// slot = local_tile * 8 + event.
+#define B200Q_PAIR_STAMP(local, event) do { if (blockIdx.x == 0 && (local) < 64) { unsigned long long t_; \
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) :: "memory"); \
+    reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(a.status) - kStatusOffset + 262144)[(local) * 8 + (event)] = t_; } } while (0)
+#else
+#define B200Q_PAIR_STAMP(local, event) do { } while (0)
+#endif
+
+constexpr int kPairStages = 6;
+
+template <Type F>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+w8a8_tcgen05_prefill_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                          const PrefillArgs a) {
+    constexpr bool kInt = F == Type::I8;
+    constexpr int BN = kPrefillTokens;               // tokens per tile (MMA N)
+    constexpr int kHalfTokens = BN / 2;               // token rows this CTA loads
+    constexpr int kWeightBytes = kBlockChannels * kBlockK, kTokenBytes = kHalfTokens * kBlockK;
+    constexpr int kStageBytes = kWeightBytes + kTokenBytes; // per CTA
+    constexpr uint32_t kRingBytes = kPairStages * kStageBytes; // the epilogue's staging patches follow the ring
+    constexpr uint32_t kIdesc = kInt ? ptx::idesc_i8(2 * kBlockChannels, BN) : ptx::idesc_e4m3(2 * kBlockChannels, BN);
+
+    extern __shared__ uint8_t dynamic_smem[];
+    __shared__ alignas(8) uint64_t full_bar[kPairStages], empty_bar[kPairStages], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    __shared__ alignas(16) float sx_tile[2][BN];
+
+    const uint32_t raw_base = ptx::smem_u32(dynamic_smem);
+    const uint32_t tiles_base = (raw_base + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair_tiles_n = (a.n + 2 * kBlockChannels - 1) / (2 * kBlockChannels), m_tiles = (a.m + BN - 1) / BN;
+    const int tiles = pair_tiles_n * m_tiles;
+    const int clusters = gridDim.x / 2, cluster_id = blockIdx.x / 2;
+    const int kb_count = (a.k + kBlockK - 1) / kBlockK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPairStages; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&acc_full[b]), 1);
+            ptx::mbar_init(ptx::smem_u32(&acc_empty[b]), 2 * (kEpilogueThreads / 32));
+        }
+        abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+    }
+    if (warp == 1) ptx::tmem_alloc_pair(ptx::smem_u32(&tmem_slot), 512);
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    ptx::cluster_sync(); // both CTAs' barriers are initialised before either signals the other
+    ptx::tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    volatile int *abort_ptr = &abort_flag;
+    ptx::launch_dependents();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&map_w);
+            ptx::prefetch_tensormap(&map_x);
+            ptx::wait_for_upstream();
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < tiles && ok; tile += clusters) {
+                const int n0 = (tile % pair_tiles_n) * 2 * kBlockChannels + int(rank) * kBlockChannels;
+                const int m0 = (tile / pair_tiles_n) * BN + int(rank) * kHalfTokens;
+                for (int kb = 0; kb < kb_count; ++kb) {
+                    if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_ptr)) { ok = false; break; }
+                    const uint32_t leader_full = ptx::map_to_rank(ptx::smem_u32(&full_bar[stage]), 0);
+                    const uint32_t dst = tiles_base + uint32_t(stage) * kStageBytes;
+                    if (leader) ptx::mbar_arrive_expect_tx(ptx::smem_u32(&full_bar[stage]), 2 * kStageBytes);
+                    ptx::tma_load_2d_pair(dst, &map_w, leader_full, kb * kBlockK, n0);
+                    ptx::tma_load_2d_pair(dst + kWeightBytes, &map_x, leader_full, kb * kBlockK, m0);
+                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && leader) {
+            int stage = 0, local = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < tiles && ok; tile += clusters, ++local) {
+                const int buffer = local & 1;
+                B200Q_PAIR_STAMP(local, 0);
+                if (!ptx::mbar_wait(ptx::smem_u32(&acc_empty[buffer]), ((uint32_t(local) >> 1) & 1u) ^ 1u, abort_ptr)) break;
+                B200Q_PAIR_STAMP(local, 1);
+                ptx::tcgen05_fence_after();
+                const uint32_t d = tmem_base + uint32_t(buffer * BN);
+                for (int kb = 0; kb < kb_count; ++kb) {
+                    if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_ptr)) { ok = false; break; }
+                    if (kb == 0) B200Q_PAIR_STAMP(local, 2);
+                    ptx::tcgen05_fence_after();
+                    const uint32_t tile_smem = tiles_base + uint32_t(stage) * kStageBytes;
+                    const uint64_t desc_w = ptx::smem_desc_k128(tile_smem), desc_x = ptx::smem_desc_k128(tile_smem + kWeightBytes);
+#pragma unroll
+                    for (int step = 0; step < kBlockK / 32; ++step) {
+                        const uint32_t accumulate = (kb > 0 || step > 0);
+                        if (kInt) ptx::mma_i8_pair(d, desc_w + uint64_t(step * 2), desc_x + uint64_t(step * 2), kIdesc, accumulate);
+                        else ptx::mma_f8_pair(d, desc_w + uint64_t(step * 2), desc_x + uint64_t(step * 2), kIdesc, accumulate);
+                    }
+                    ptx::tcgen05_commit_pair(ptx::smem_u32(&empty_bar[stage]), 3);
+                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) ptx::tcgen05_commit_pair(ptx::smem_u32(&acc_full[buffer]), 3);
+                B200Q_PAIR_STAMP(local, 3);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps (both CTAs)
+        const int e_thread = threadIdx.x - 64;
+        const int quadrant = warp & 3, half = (warp - 2) >> 2;
+        const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16);
+        const float *__restrict__ residual = a.residual_f32;
+        uint16_t *patches = reinterpret_cast<uint16_t *>(dynamic_smem + (tiles_base - raw_base) + kRingBytes);
+        ptx::wait_for_upstream();
+        int local = 0;
+        for (int tile = cluster_id; tile < tiles; tile += clusters, ++local) {
+            const int buffer = local & 1;
+            const int n0 = (tile % pair_tiles_n) * 2 * kBlockChannels + int(rank) * kBlockChannels;
+            const int m0 = (tile / pair_tiles_n) * BN;
+            const int valid_tokens = min(BN, a.m - m0);
+            const int n = n0 + quadrant * 32 + lane;
+            const float scale_w = n < a.n ? a.sw[n] : 0.f;
+            sx_tile[buffer][e_thread] = e_thread < valid_tokens ? a.sx[m0 + e_thread] : 0.f;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (e_thread == 0) B200Q_PAIR_STAMP(local, 4);
+            if (!ptx::mbar_wait(ptx::smem_u32(&acc_full[buffer]), (uint32_t(local) >> 1) & 1u, abort_ptr)) break;
+            if (e_thread == 0) B200Q_PAIR_STAMP(local, 5);
+            ptx::tcgen05_fence_after();
+#pragma unroll 1
+            for (int chunk = half; chunk < BN / 16; chunk += 2) {
+                if (chunk * 16 >= valid_tokens) break;
+                uint32_t r[16];
+#if defined(B200Q_EXP) && B200Q_EXP == 2
+#pragma unroll
+                for (int i = 0; i < 16; ++i) r[i] = uint32_t(chunk + i + lane);
+#else
+                ptx::tmem_load16(lane_base + uint32_t(buffer * BN + chunk * 16), r);
+                ptx::tmem_load_wait();
+#endif
+                prefill_store_chunk<kInt>(a, r, &sx_tile[buffer][chunk * 16], scale_w, residual, m0 + chunk * 16, n0,
+                                          valid_tokens - chunk * 16, quadrant, lane, half,
+                                          patches + ((half * 2 + ((chunk >> 1) & 1)) * 16 * kBlockChannels));
+            }
+            // Hand the accumulator back to the leader's MMA issuer (remote arrive from the peer CTA).
+            ptx::tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_rank(ptx::smem_u32(&acc_empty[buffer]), 0));
+            if (e_thread == 0) B200Q_PAIR_STAMP(local, 6);
+        }
+        ptx::tcgen05_fence_before();
+    }
+
+    // Neither CTA may leave while the other can still signal its barriers or read its shared memory.
+    __syncthreads();
+    ptx::cluster_sync();
+    if (warp == 1) {
+        ptx::tcgen05_fence_after();
+        ptx::tmem_dealloc_pair(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 && abort_flag) atomicExch(a.status, 1 + int(blockIdx.x));
+}
+} // namespace tts::b200

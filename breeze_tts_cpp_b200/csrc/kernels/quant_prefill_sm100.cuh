@@ -20,6 +20,7 @@ namespace tts::b200 {
 
 constexpr int kPrefillTokens = 256;
 constexpr int kPrefillStages = 4;
+constexpr int kPrefillPatchBytes = 2 * 2 * 16 * kBlockChannels * 2; // two chunk groups x two parities x [16][128] 16-bit
 
 struct PrefillArgs {
     int m, n, k;
@@ -30,6 +31,60 @@ struct PrefillArgs {
     int *status;
 };
 
+// One 16-token chunk of a tile's epilogue, executed by the four warps (one per tensor-memory lane
+// quadrant) that share a chunk. Phase 1, lane = channel: accumulator -> (acc*sx)*sw (+ fp32 residual)
+// -> 16-bit, written to a small shared-memory patch [token][channel]. After a 128-thread barrier,
+// phase 2, lane = four consecutive channels: every warp copies four token rows of the patch to
+// global memory as 8-byte stores, 256 contiguous bytes per row. The patch is double-buffered so one
+// barrier per chunk suffices. `r` holds the chunk's 16 accumulator words of this lane.
+template <bool kInt>
+__device__ __forceinline__ void prefill_store_chunk(const PrefillArgs &a, const uint32_t (&r)[16], const float *sx_chunk,
+                                                    float scale_w, const float *__restrict__ residual, int m_first,
+                                                    int n_tile0, int valid_rows, int quadrant, int lane, int group,
+                                                    uint16_t *patch /* [16][128] of this group and parity */) {
+    const int channel = quadrant * 32 + lane, n = n_tile0 + channel;
+    const bool bf16_out = a.out_type == int(Type::BF16);
+    // All loads (activation scales from shared memory, residuals from global memory) come first: a
+    // load may not be moved above an earlier store it might alias, so interleaving them with the patch
+    // stores would serialise sixteen round trips.
+    float scale_x[16], skip[16];
+    {
+        const float4 *sx4 = reinterpret_cast<const float4 *>(sx_chunk);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 v = sx4[q];
+            scale_x[4 * q] = v.x; scale_x[4 * q + 1] = v.y; scale_x[4 * q + 2] = v.z; scale_x[4 * q + 3] = v.w;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+        skip[i] = (residual && n < a.n && i < valid_rows) ? __ldg(residual + size_t(m_first + i) * a.n + n) : 0.f;
+    uint16_t bits[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float acc = kInt ? float(int(r[i])) : __uint_as_float(r[i]);
+        float value = __fmul_rn(__fmul_rn(acc, scale_x[i]), scale_w);
+        if (residual) value = __fadd_rn(value, skip[i]);
+        if (bf16_out) { __nv_bfloat16 b = __float2bfloat16_rn(value); bits[i] = *reinterpret_cast<uint16_t *>(&b); }
+        else { __half h = __float2half_rn(value); bits[i] = *reinterpret_cast<uint16_t *>(&h); }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) patch[i * kBlockChannels + channel] = bits[i];
+    if (group == 0) asm volatile("bar.sync 2, 128;" ::: "memory");
+    else asm volatile("bar.sync 3, 128;" ::: "memory");
+    const int n4 = n_tile0 + lane * 4;
+    if (n4 < a.n) {
+#pragma unroll
+        for (int rr = 0; rr < 4; ++rr) {
+            const int i = quadrant * 4 + rr;
+            if (i < valid_rows) {
+                const uint2 four = *reinterpret_cast<const uint2 *>(patch + i * kBlockChannels + lane * 4);
+                *reinterpret_cast<uint2 *>(static_cast<uint16_t *>(a.out) + size_t(m_first + i) * a.n + n4) = four;
+            }
+        }
+    }
+}
+
 template <Type F>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 w8a8_tcgen05_prefill(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -38,13 +93,14 @@ w8a8_tcgen05_prefill(const __grid_constant__ CUtensorMap map_w, const __grid_con
     constexpr int BN = kPrefillTokens;
     constexpr int kWeightBytes = kBlockChannels * kBlockK, kTokenBytes = BN * kBlockK;
     constexpr int kStageBytes = kWeightBytes + kTokenBytes;
+    constexpr uint32_t kRingBytes = kPrefillStages * kStageBytes; // the epilogue's staging patches follow the ring
     constexpr uint32_t kIdesc = kInt ? ptx::idesc_i8(kBlockChannels, BN) : ptx::idesc_e4m3(kBlockChannels, BN);
 
     extern __shared__ uint8_t dynamic_smem[];
     __shared__ alignas(8) uint64_t full_bar[kPrefillStages], empty_bar[kPrefillStages], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
-    __shared__ float sx_tile[2][BN]; // activation scales of the tile in each accumulator
+    __shared__ alignas(16) float sx_tile[2][BN]; // activation scales of the tile in each accumulator
 
     const uint32_t raw_base = ptx::smem_u32(dynamic_smem);
     const uint32_t tiles_base = (raw_base + 1023u) & ~1023u;
@@ -129,18 +185,17 @@ w8a8_tcgen05_prefill(const __grid_constant__ CUtensorMap map_w, const __grid_con
         // ------------------------------------------------------------ epilogue warps
         const int e_thread = threadIdx.x - 64;
         const int quadrant = warp & 3, half = (warp - 2) >> 2;
-        const int channel_in_tile = quadrant * 32 + lane;
         const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16);
-        const bool bf16_out = a.out_type == int(Type::BF16);
+        const float *__restrict__ residual = a.residual_f32;
+        uint16_t *patches = reinterpret_cast<uint16_t *>(dynamic_smem + (tiles_base - raw_base) + kRingBytes);
         ptx::wait_for_upstream();
         int local = 0;
         for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
             const int buffer = local & 1;
             const int n0 = (tile % n_tiles) * kBlockChannels, m0 = (tile / n_tiles) * BN;
             const int valid_tokens = min(BN, a.m - m0);
-            const int n = n0 + channel_in_tile;
-            const bool channel_ok = n < a.n;
-            const float scale_w = channel_ok ? a.sw[n] : 0.f;
+            const int n = n0 + quadrant * 32 + lane;
+            const float scale_w = n < a.n ? a.sw[n] : 0.f;
             // Stage this tile's activation scales while the tensor cores are still busy with it.
             sx_tile[buffer][e_thread] = e_thread < valid_tokens ? a.sx[m0 + e_thread] : 0.f;
             asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -152,20 +207,9 @@ w8a8_tcgen05_prefill(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 uint32_t r[16];
                 ptx::tmem_load16(lane_base + uint32_t(buffer * BN + chunk * 16), r);
                 ptx::tmem_load_wait();
-                if (channel_ok) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int c = chunk * 16 + i;
-                        if (c < valid_tokens) {
-                            const size_t at = size_t(m0 + c) * a.n + n;
-                            const float acc = kInt ? float(int(r[i])) : __uint_as_float(r[i]);
-                            float value = __fmul_rn(__fmul_rn(acc, sx_tile[buffer][c]), scale_w);
-                            if (a.residual_f32) value = __fadd_rn(value, a.residual_f32[at]);
-                            if (bf16_out) static_cast<__nv_bfloat16 *>(a.out)[at] = __float2bfloat16_rn(value);
-                            else static_cast<__half *>(a.out)[at] = __float2half_rn(value);
-                        }
-                    }
-                }
+                prefill_store_chunk<kInt>(a, r, &sx_tile[buffer][chunk * 16], scale_w, residual, m0 + chunk * 16, n0,
+                                          valid_tokens - chunk * 16, quadrant, lane, half,
+                                          patches + ((half * 2 + ((chunk >> 1) & 1)) * 16 * kBlockChannels));
             }
             // This warp has read everything it needs from the accumulator: hand it back.
             ptx::tcgen05_fence_before();
