@@ -63,12 +63,14 @@ struct FusedEpilogue {
 // records to a log 64 KiB into the workspace when it exits; word 0 of the log is the record count.
 #define B200Q_STAMP(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { \
     unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) :: "memory"); stamp_log[slot] = t_; } } while (0)
+#define B200Q_CLOCK(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) stamp_log[slot] = (unsigned long long)clock64(); } while (0)
 #define B200Q_STAMP_FLUSH() do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { \
     unsigned long long *log_ = reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(a.status) - kStatusOffset + 65536); \
-    unsigned long long at_ = atomicAdd(log_, 12ull); \
-    if (at_ < 60000) for (int s_ = 0; s_ < 12; ++s_) { log_[1 + 2 * (at_ + s_)] = (unsigned long long)(a.n) << 32 | (unsigned long long)(s_); log_[2 + 2 * (at_ + s_)] = stamp_log[s_]; } } } while (0)
+    unsigned long long at_ = atomicAdd(log_, 28ull); \
+    if (at_ < 60000) for (int s_ = 0; s_ < 28; ++s_) { log_[1 + 2 * (at_ + s_)] = (unsigned long long)(a.n) << 32 | (unsigned long long)(s_); log_[2 + 2 * (at_ + s_)] = stamp_log[s_]; } } } while (0)
 #else
 #define B200Q_STAMP(slot) do { } while (0)
+#define B200Q_CLOCK(slot) do { } while (0)
 #define B200Q_STAMP_FLUSH() do { } while (0)
 #endif
 
@@ -132,7 +134,7 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi, int type) {
 template <Type F, bool Grouped, int BN>
 __global__ void __launch_bounds__(kGemmThreads, (!Grouped && BN <= 64) ? 2 : 1)
 w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                  const GemmArgs a) {
+                  const __grid_constant__ GemmArgs a) {
     constexpr bool kInt = F == Type::I8;
     constexpr bool kIntAcc = kInt && !Grouped; // partial tiles / raw outputs carry int32 bit patterns
     constexpr int kWeightBytes = kBlockChannels * kBlockK, kTokenBytes = BN * kBlockK;
@@ -146,13 +148,13 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     constexpr uint32_t kPassBytes = kRowsPerPass * kBlockChannels * 4;
 
     extern __shared__ uint8_t dynamic_smem[];
-    __shared__ alignas(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], acc_full[2], acc_empty[2];
+    __shared__ alignas(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], acc_full[2], acc_empty[2], x_full;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ float sx_tile[BN]; // per-row activation scales of this token tile
 #ifdef B200Q_TIMING
-    __shared__ unsigned long long stamp_log[12];
-    if (threadIdx.x < 12) stamp_log[threadIdx.x] = 0;
+    __shared__ unsigned long long stamp_log[28];
+    if (threadIdx.x < 28) stamp_log[threadIdx.x] = 0;
     __syncthreads();
 #endif
 
@@ -190,6 +192,7 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             ptx::mbar_init(ptx::smem_u32(&acc_full[b]), 1);
             ptx::mbar_init(ptx::smem_u32(&acc_empty[b]), kEpilogueThreads / 32);
         }
+        ptx::mbar_init(ptx::smem_u32(&x_full), 1);
         abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async_smem();
@@ -210,19 +213,22 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         if (lane == 0) {
             ptx::prefetch_tensormap(&map_w);
             ptx::prefetch_tensormap(&map_x);
-            // Weights do not depend on the upstream kernel: fill the ring with weight tiles first,
-            // then wait for upstream and add the activation tiles to the same stages.
+            // Weights do not depend on the upstream kernel: fill the ring with weight tiles first
+            // (one barrier per stage), then wait for upstream and add the activation tiles of all
+            // those stages under ONE barrier. A barrier test between MMA issues costs the issuing
+            // thread about 200 cycles, so the burst over the prefetched stages must not need any.
             const int ahead = min(a.stages, kb_count);
             for (int i = 0; i < ahead; ++i) {
                 const uint32_t bar = ptx::smem_u32(&full_bar[i]);
-                ptx::mbar_arrive_expect_tx(bar, kStageBytes);
+                ptx::mbar_arrive_expect_tx(bar, kWeightBytes);
                 ptx::tma_load_2d(tiles_base + uint32_t(i) * kStageBytes, &map_w, bar, (kb_begin + i) * kBlockK, n0);
             }
             ptx::wait_for_upstream();
             B200Q_STAMP(9);
+            ptx::mbar_arrive_expect_tx(ptx::smem_u32(&x_full), uint32_t(ahead) * kTokenBytes);
             for (int i = 0; i < ahead; ++i)
                 ptx::tma_load_2d(tiles_base + uint32_t(i) * kStageBytes + kWeightBytes, &map_x,
-                                 ptx::smem_u32(&full_bar[i]), (kb_begin + i) * kBlockK, m0);
+                                 ptx::smem_u32(&x_full), (kb_begin + i) * kBlockK, m0);
             int stage = ahead == a.stages ? 0 : ahead;
             uint32_t phase = ahead == a.stages ? 1u : 0u;
             for (int kb = kb_begin + ahead; kb < kb_end; ++kb) {
@@ -238,32 +244,65 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         if (splits > 1) ptx::cluster_wait();
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            for (int it = 0; it < kb_count; ++it) {
+        // The whole warp runs the loop so that stage indices and descriptors stay warp-uniform (the
+        // tensor-core instructions take them from uniform registers); one elected lane issues.
+        {
+            // The weight tiles of the prefetched stages land while the upstream kernel still runs:
+            // collect those barriers now, off the critical path, then wait once for the activations.
+            const int ahead = min(a.stages, kb_count);
+            bool ok = true;
+            for (int i = 0; i < ahead && ok; ++i) ok = ptx::mbar_wait(ptx::smem_u32(&full_bar[i]), 0u, abort_ptr);
+            ok = ok && ptx::mbar_wait(ptx::smem_u32(&x_full), 0u, abort_ptr);
+            ok = __all_sync(0xffffffffu, ok);
+            if (lane == 0) { B200Q_STAMP(2); B200Q_CLOCK(10); }
+            // Per-row scales: the prefetched stages need no barrier at all any more, so their MMAs go
+            // out back to back (any shared-memory access between MMA issues stalls the issuing warp for
+            // a couple of hundred cycles). Stage i holds K block i here.
+            int first = 0;
+            if (!Grouped && ok) {
+                ptx::tcgen05_fence_after();
+                for (int it = 0; it < ahead; ++it) {
+                    const uint32_t tile = tiles_base + uint32_t(it) * kStageBytes;
+                    if (ptx::elect_one()) {
+                        if (kInt) ptx::mma_i8_k128(tmem_base, ptx::smem_desc_lo_k128(tile), ptx::smem_desc_lo_k128(tile + kWeightBytes), kIdesc, it > 0);
+                        else ptx::mma_f8_k128(tmem_base, ptx::smem_desc_lo_k128(tile), ptx::smem_desc_lo_k128(tile + kWeightBytes), kIdesc, it > 0);
+                        // Only a stage that will be refilled needs to report that its MMAs retired.
+                        if (it + a.stages < kb_count) ptx::tcgen05_commit(ptx::smem_u32(&empty_bar[it]));
+                    }
+                    __syncwarp();
+                }
+                first = ahead;
+            }
+            if (lane == 0) B200Q_CLOCK(12);
+            int stage = first == a.stages ? 0 : first;
+            uint32_t phase = first == a.stages ? 1u : 0u;
+            // Refilled stages arrive at the rate memory delivers them, one barrier each.
+            for (int it = first; it < kb_count && ok; ++it) {
                 const int buffer = Grouped ? (it & 1) : 0;
-                if (Grouped && !ptx::mbar_wait(ptx::smem_u32(&acc_empty[buffer]), ((uint32_t(it) >> 1) & 1u) ^ 1u, abort_ptr))
-                    break;
-                if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_ptr)) break;
-                if (it == 0) B200Q_STAMP(2);
+                if (Grouped) ok = ptx::mbar_wait(ptx::smem_u32(&acc_empty[buffer]), ((uint32_t(it) >> 1) & 1u) ^ 1u, abort_ptr);
+                if (it >= ahead) ok = ok && ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_ptr);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
                 ptx::tcgen05_fence_after();
                 const uint32_t tile = tiles_base + uint32_t(stage) * kStageBytes;
-                const uint64_t desc_w = ptx::smem_desc_k128(tile), desc_x = ptx::smem_desc_k128(tile + kWeightBytes);
+                const uint32_t lo_w = ptx::smem_desc_lo_k128(tile), lo_x = ptx::smem_desc_lo_k128(tile + kWeightBytes);
                 const uint32_t d = tmem_base + uint32_t(buffer * BN);
-#pragma unroll
-                for (int step = 0; step < kBlockK / 32; ++step) {
-                    const uint32_t accumulate = Grouped ? (step > 0) : (it > 0 || step > 0);
-                    // 32 bytes of K per MMA: +2 in the descriptor's 16-byte address units.
-                    if (kInt) ptx::mma_i8(d, desc_w + uint64_t(step * 2), desc_x + uint64_t(step * 2), kIdesc, accumulate);
-                    else ptx::mma_f8(d, desc_w + uint64_t(step * 2), desc_x + uint64_t(step * 2), kIdesc, accumulate);
+                if (ptx::elect_one()) {
+                    const uint32_t accumulate = Grouped ? 0u : uint32_t(it > 0);
+                    if (kInt) ptx::mma_i8_k128(d, lo_w, lo_x, kIdesc, accumulate);
+                    else ptx::mma_f8_k128(d, lo_w, lo_x, kIdesc, accumulate);
+                    if (it + a.stages < kb_count) ptx::tcgen05_commit(ptx::smem_u32(&empty_bar[stage]));
+                    if (Grouped) ptx::tcgen05_commit(ptx::smem_u32(&acc_full[buffer]));
                 }
-                ptx::tcgen05_commit(ptx::smem_u32(&empty_bar[stage]));
-                if (Grouped) ptx::tcgen05_commit(ptx::smem_u32(&acc_full[buffer]));
+                __syncwarp();
                 if (++stage == a.stages) { stage = 0; phase ^= 1u; }
             }
-            if (!Grouped) ptx::tcgen05_commit(ptx::smem_u32(&acc_full[0]));
-            B200Q_STAMP(3);
+            if (lane == 0) B200Q_CLOCK(11);
+            if (ptx::elect_one()) {
+                if (!Grouped) ptx::tcgen05_commit(ptx::smem_u32(&acc_full[0]));
+            }
+            __syncwarp();
+            if (lane == 0) B200Q_STAMP(3);
         }
         if (splits > 1) ptx::cluster_wait();
     } else {

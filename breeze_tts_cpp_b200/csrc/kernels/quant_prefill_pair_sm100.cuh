@@ -166,13 +166,8 @@ w8a8_tcgen05_prefill_pair(const __grid_constant__ CUtensorMap map_w, const __gri
             for (int chunk = half; chunk < BN / 16; chunk += 2) {
                 if (chunk * 16 >= valid_tokens) break;
                 uint32_t r[16];
-#if defined(B200Q_EXP) && B200Q_EXP == 2
-#pragma unroll
-                for (int i = 0; i < 16; ++i) r[i] = uint32_t(chunk + i + lane);
-#else
                 ptx::tmem_load16(lane_base + uint32_t(buffer * BN + chunk * 16), r);
                 ptx::tmem_load_wait();
-#endif
                 prefill_store_chunk<kInt>(a, r, &sx_tile[buffer][chunk * 16], scale_w, residual, m0 + chunk * 16, n0,
                                           valid_tokens - chunk * 16, quadrant, lane, half,
                                           patches + ((half * 2 + ((chunk >> 1) & 1)) * 16 * kBlockChannels));

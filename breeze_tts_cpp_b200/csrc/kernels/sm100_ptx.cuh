@@ -242,6 +242,61 @@ __device__ __forceinline__ uint64_t smem_desc_k128(uint32_t smem_addr) {
     d |= uint64_t(2) << 61;
     return d;
 }
+// The same descriptor as two 32-bit halves. Only the low half (start address) changes from tile to
+// tile and from K step to K step, so an issue loop that carries the halves separately keeps the high
+// half loop-invariant and steps the low half with 32-bit adds.
+constexpr uint32_t kDescHiK128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t smem_desc_lo_k128(uint32_t smem_addr) {
+    return ((smem_addr & 0x3ffffu) >> 4) | (1u << 16);
+}
+__device__ __forceinline__ void mma_i8_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, p;\n\t}" ::"r"(d_tmem),
+                 "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiK128)
+                 : "memory");
+}
+__device__ __forceinline__ void mma_f8_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %3, p;\n\t}" ::"r"(d_tmem),
+                 "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiK128)
+                 : "memory");
+}
+// The four MMAs that consume one 128-byte K block (32 bytes of K each: +2 descriptor units per
+// step), issued from one instruction block so that no other code separates them. `accumulate`
+// applies to the first; the other three always add to it.
+#define B200Q_MMA_K128(NAME, KIND)                                                                             \
+    __device__ __forceinline__ void NAME(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,         \
+                                         uint32_t accumulate) {                                                \
+        asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t.reg .b32 al, bl;\n\t"                      \
+                     "setp.ne.b32 p, %4, 0;\n\t"                                                               \
+                     "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"                                      \
+                     "tcgen05.mma.cta_group::1.kind::" KIND " [%0], da, db, %3, p;\n\t"                         \
+                     "setp.ne.b32 p, %3, 0;\n\t"                                                               \
+                     "add.u32 al, %1, 2;\n\tadd.u32 bl, %2, 2;\n\t"                                            \
+                     "mov.b64 da, {al, %5};\n\tmov.b64 db, {bl, %5};\n\t"                                      \
+                     "tcgen05.mma.cta_group::1.kind::" KIND " [%0], da, db, %3, p;\n\t"                         \
+                     "add.u32 al, %1, 4;\n\tadd.u32 bl, %2, 4;\n\t"                                            \
+                     "mov.b64 da, {al, %5};\n\tmov.b64 db, {bl, %5};\n\t"                                      \
+                     "tcgen05.mma.cta_group::1.kind::" KIND " [%0], da, db, %3, p;\n\t"                         \
+                     "add.u32 al, %1, 6;\n\tadd.u32 bl, %2, 6;\n\t"                                            \
+                     "mov.b64 da, {al, %5};\n\tmov.b64 db, {bl, %5};\n\t"                                      \
+                     "tcgen05.mma.cta_group::1.kind::" KIND " [%0], da, db, %3, p;\n\t}" ::"r"(d_tmem),          \
+                     "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiK128)                        \
+                     : "memory");                                                                              \
+    }
+B200Q_MMA_K128(mma_i8_k128, "i8")
+B200Q_MMA_K128(mma_f8_k128, "f8f6f4")
+#undef B200Q_MMA_K128
+// One lane of a converged warp; the same lane every time for the same mask.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t elected;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(elected));
+    return elected != 0;
+}
 // Instruction descriptor: D format at bits 4-5 (1 = f32, 2 = s32), A/B formats at 7-9 / 10-12,
 // both operands K-major, N>>3 at bits 17-22, M>>4 at bits 24-28.
 __host__ __device__ constexpr uint32_t idesc_i8(int m, int n) {
