@@ -5,6 +5,7 @@
 #include "kernels/quant_linear_sm100.cuh"
 #include "kernels/quant_prefill_sm100.cuh"
 #include "kernels/quant_prefill_pair_sm100.cuh"
+#include "kernels/quant_prefill_grouped_sm100.cuh"
 #include "ops/epilogue.h"
 #include <cuda.h>
 #include <cstdlib>
@@ -63,6 +64,32 @@ const CUtensorMap &tensor_map(const void *base, int rows, int k, int box_rows, b
                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (status != CUDA_SUCCESS)
         throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(status)));
+    if (cache.size() > 4096) cache.clear();
+    return cache.emplace(key, map).first->second;
+}
+
+// Group-major fp32 scales [K/128, rows]: box = 128 consecutive rows of one K group, no swizzle,
+// rows past the end read as zero.
+const CUtensorMap &scale_map(const float *base, int rows, int groups) {
+    using Key = std::tuple<const void *, int, int>;
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex guard;
+    std::lock_guard<std::mutex> lock(guard);
+    Key key{base, rows, groups};
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    if (reinterpret_cast<uintptr_t>(base) % 16 || rows % 4)
+        throw std::invalid_argument("K-group scales must be 16-byte aligned with a row count that is a multiple of 4");
+    CUtensorMap map;
+    cuuint64_t dims[2] = {cuuint64_t(rows), cuuint64_t(groups)};
+    cuuint64_t strides[1] = {cuuint64_t(rows) * 4};
+    cuuint32_t box[2] = {cuuint32_t(kGroupedTokens), 1};
+    cuuint32_t element_strides[2] = {1, 1};
+    CUresult status = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides,
+                                     box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (status != CUDA_SUCCESS)
+        throw std::runtime_error("cuTensorMapEncodeTiled (scales) failed with code " + std::to_string(int(status)));
     if (cache.size() > 4096) cache.clear();
     return cache.emplace(key, map).first->second;
 }
@@ -189,7 +216,28 @@ void launch_prefill_pair(const CUtensorMap &map_w, const CUtensorMap &map_x, con
     check(cudaLaunchKernelEx(&config, w8a8_tcgen05_prefill_pair<F>, map_w, map_x, args), "quantized pair GEMM launch");
 }
 
+// Persistent K-group kernel: one CTA per multiprocessor over 128x128 tiles.
+template <Type F>
+void launch_prefill_grouped(const CUtensorMap &map_w, const CUtensorMap &map_x, const CUtensorMap &map_sw,
+                            const CUtensorMap &map_sx, const PrefillArgs &args, cudaStream_t stream) {
+    const int tiles = ((args.n + kBlockChannels - 1) / kBlockChannels) * ((args.m + kGroupedTokens - 1) / kGroupedTokens);
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(unsigned(std::min(tiles, multiprocessor_count())));
+    config.blockDim = dim3(kGroupedThreads);
+    config.dynamicSmemBytes = kGroupedSmem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    check(cudaLaunchKernelEx(&config, w8a8_tcgen05_prefill_grouped<F>, map_w, map_x, map_sw, map_sx, args),
+          "quantized K-group prefill GEMM launch");
+}
+
 template <Type F> void raise_limits() {
+    check(cudaFuncSetAttribute(w8a8_tcgen05_prefill_grouped<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kGroupedSmem)),
+          "cudaFuncSetAttribute(shared memory)");
     check(cudaFuncSetAttribute(w8a8_tcgen05_prefill_pair<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kPairSmem)),
           "cudaFuncSetAttribute(shared memory)");
     check(cudaFuncSetAttribute(w8a8_tcgen05_prefill<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kPrefillSmem)),
@@ -361,6 +409,19 @@ void launch_quant_linear(LinearPath config, KernelProblem shape, const void *inp
         const CUtensorMap &map_x = tensor_map(input, shape.rows, shape.reduction, bn, false);
         if (format == Type::I8) launch_prefill<Type::I8>(map_w, map_x, prefill, stream);
         else launch_prefill<Type::FP8>(map_w, map_x, prefill, stream);
+        return;
+    }
+    // Compute-bound K-group shapes (both operands grouped by 128, enough 128x128 tiles to fill most of
+    // the GPU, plain epilogue) take the persistent K-group kernel; it never splits K.
+    if (grouped && shape.input_group == kBlockK && shape.weight_group == kBlockK && bn == kGroupedTokens &&
+        !args.ep.chain && args.vector_io && shape.rows % 4 == 0 &&
+        int64_t(n_tiles) * ((shape.rows + kGroupedTokens - 1) / kGroupedTokens) >= int64_t(multiprocessor_count()) * 2 / 3) {
+        PrefillArgs prefill{args.m, args.n, args.k, xs, ws, y, int(output_type), args.ep.residual_f32, args.status};
+        const CUtensorMap &map_x = tensor_map(input, shape.rows, shape.reduction, kGroupedTokens, false);
+        const CUtensorMap &map_sw = scale_map(ws, shape.channels, kb_total);
+        const CUtensorMap &map_sx = scale_map(xs, shape.rows, kb_total);
+        if (format == Type::I8) launch_prefill_grouped<Type::I8>(map_w, map_x, map_sw, map_sx, prefill, stream);
+        else launch_prefill_grouped<Type::FP8>(map_w, map_x, map_sw, map_sx, prefill, stream);
         return;
     }
     const CUtensorMap &map_x = tensor_map(input, shape.rows, shape.reduction, bn, false);

@@ -110,34 +110,39 @@ w8a8_tcgen05_prefill_pair(const __grid_constant__ CUtensorMap map_w, const __gri
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
-        if (lane == 0 && leader) {
+        // The whole warp runs the loop (warp-uniform stage arithmetic); one elected lane issues the
+        // four MMAs of a K block from a single instruction block and commits.
+        if (leader) {
             int stage = 0, local = 0;
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = cluster_id; tile < tiles && ok; tile += clusters, ++local) {
                 const int buffer = local & 1;
-                B200Q_PAIR_STAMP(local, 0);
-                if (!ptx::mbar_wait(ptx::smem_u32(&acc_empty[buffer]), ((uint32_t(local) >> 1) & 1u) ^ 1u, abort_ptr)) break;
-                B200Q_PAIR_STAMP(local, 1);
+                if (lane == 0) B200Q_PAIR_STAMP(local, 0);
+                ok = ptx::mbar_wait(ptx::smem_u32(&acc_empty[buffer]), ((uint32_t(local) >> 1) & 1u) ^ 1u, abort_ptr);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (lane == 0) B200Q_PAIR_STAMP(local, 1);
                 ptx::tcgen05_fence_after();
                 const uint32_t d = tmem_base + uint32_t(buffer * BN);
                 for (int kb = 0; kb < kb_count; ++kb) {
-                    if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_ptr)) { ok = false; break; }
-                    if (kb == 0) B200Q_PAIR_STAMP(local, 2);
+                    ok = __all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_ptr));
+                    if (!ok) break;
+                    if (kb == 0 && lane == 0) B200Q_PAIR_STAMP(local, 2);
                     ptx::tcgen05_fence_after();
                     const uint32_t tile_smem = tiles_base + uint32_t(stage) * kStageBytes;
-                    const uint64_t desc_w = ptx::smem_desc_k128(tile_smem), desc_x = ptx::smem_desc_k128(tile_smem + kWeightBytes);
-#pragma unroll
-                    for (int step = 0; step < kBlockK / 32; ++step) {
-                        const uint32_t accumulate = (kb > 0 || step > 0);
-                        if (kInt) ptx::mma_i8_pair(d, desc_w + uint64_t(step * 2), desc_x + uint64_t(step * 2), kIdesc, accumulate);
-                        else ptx::mma_f8_pair(d, desc_w + uint64_t(step * 2), desc_x + uint64_t(step * 2), kIdesc, accumulate);
+                    const uint32_t lo_w = ptx::smem_desc_lo_k128(tile_smem), lo_x = ptx::smem_desc_lo_k128(tile_smem + kWeightBytes);
+                    if (ptx::elect_one()) {
+                        if (kInt) ptx::mma_i8_pair_k128(d, lo_w, lo_x, kIdesc, uint32_t(kb > 0));
+                        else ptx::mma_f8_pair_k128(d, lo_w, lo_x, kIdesc, uint32_t(kb > 0));
+                        ptx::tcgen05_commit_pair(ptx::smem_u32(&empty_bar[stage]), 3);
                     }
-                    ptx::tcgen05_commit_pair(ptx::smem_u32(&empty_bar[stage]), 3);
+                    __syncwarp();
                     if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
                 }
-                if (ok) ptx::tcgen05_commit_pair(ptx::smem_u32(&acc_full[buffer]), 3);
-                B200Q_PAIR_STAMP(local, 3);
+                if (ok && ptx::elect_one()) ptx::tcgen05_commit_pair(ptx::smem_u32(&acc_full[buffer]), 3);
+                __syncwarp();
+                if (lane == 0) B200Q_PAIR_STAMP(local, 3);
             }
         }
     } else {

@@ -154,31 +154,35 @@ w8a8_tcgen05_prefill(const __grid_constant__ CUtensorMap map_w, const __grid_con
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // The whole warp runs the loop (warp-uniform stage arithmetic); one elected lane issues the
+        // four MMAs of a K block from a single instruction block and commits.
+        {
             int stage = 0, local = 0;
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
                 const int buffer = local & 1;
                 // The epilogue must have drained this accumulator (two tiles ago).
-                if (!ptx::mbar_wait(ptx::smem_u32(&acc_empty[buffer]), ((uint32_t(local) >> 1) & 1u) ^ 1u, abort_ptr)) break;
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&acc_empty[buffer]), ((uint32_t(local) >> 1) & 1u) ^ 1u, abort_ptr));
+                if (!ok) break;
                 ptx::tcgen05_fence_after();
                 const uint32_t d = tmem_base + uint32_t(buffer * BN);
                 for (int kb = 0; kb < kb_count; ++kb) {
-                    if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_ptr)) { ok = false; break; }
+                    ok = __all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_ptr));
+                    if (!ok) break;
                     ptx::tcgen05_fence_after();
                     const uint32_t tile_smem = tiles_base + uint32_t(stage) * kStageBytes;
-                    const uint64_t desc_w = ptx::smem_desc_k128(tile_smem), desc_x = ptx::smem_desc_k128(tile_smem + kWeightBytes);
-#pragma unroll
-                    for (int step = 0; step < kBlockK / 32; ++step) {
-                        const uint32_t accumulate = (kb > 0 || step > 0);
-                        if (kInt) ptx::mma_i8(d, desc_w + uint64_t(step * 2), desc_x + uint64_t(step * 2), kIdesc, accumulate);
-                        else ptx::mma_f8(d, desc_w + uint64_t(step * 2), desc_x + uint64_t(step * 2), kIdesc, accumulate);
+                    const uint32_t lo_w = ptx::smem_desc_lo_k128(tile_smem), lo_x = ptx::smem_desc_lo_k128(tile_smem + kWeightBytes);
+                    if (ptx::elect_one()) {
+                        if (kInt) ptx::mma_i8_k128(d, lo_w, lo_x, kIdesc, uint32_t(kb > 0));
+                        else ptx::mma_f8_k128(d, lo_w, lo_x, kIdesc, uint32_t(kb > 0));
+                        ptx::tcgen05_commit(ptx::smem_u32(&empty_bar[stage]));
                     }
-                    ptx::tcgen05_commit(ptx::smem_u32(&empty_bar[stage]));
+                    __syncwarp();
                     if (++stage == kPrefillStages) { stage = 0; phase ^= 1u; }
                 }
-                if (ok) ptx::tcgen05_commit(ptx::smem_u32(&acc_full[buffer]));
+                if (ok && ptx::elect_one()) ptx::tcgen05_commit(ptx::smem_u32(&acc_full[buffer]));
+                __syncwarp();
             }
         }
     } else {

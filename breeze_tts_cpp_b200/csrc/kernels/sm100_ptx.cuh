@@ -267,30 +267,45 @@ __device__ __forceinline__ void mma_f8_lo(uint32_t d_tmem, uint32_t a_lo, uint32
 }
 // The four MMAs that consume one 128-byte K block (32 bytes of K each: +2 descriptor units per
 // step), issued from one instruction block so that no other code separates them. `accumulate`
-// applies to the first; the other three always add to it.
-#define B200Q_MMA_K128(NAME, KIND)                                                                             \
+// applies to the first; the other three always add to it (the instruction descriptor is never zero,
+// which is what the second predicate test relies on).
+#define B200Q_MMA_K128(NAME, GROUP, KIND)                                                                      \
     __device__ __forceinline__ void NAME(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,         \
                                          uint32_t accumulate) {                                                \
         asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t.reg .b32 al, bl;\n\t"                      \
                      "setp.ne.b32 p, %4, 0;\n\t"                                                               \
                      "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"                                      \
-                     "tcgen05.mma.cta_group::1.kind::" KIND " [%0], da, db, %3, p;\n\t"                         \
+                     "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %3, p;\n\t"                 \
                      "setp.ne.b32 p, %3, 0;\n\t"                                                               \
                      "add.u32 al, %1, 2;\n\tadd.u32 bl, %2, 2;\n\t"                                            \
                      "mov.b64 da, {al, %5};\n\tmov.b64 db, {bl, %5};\n\t"                                      \
-                     "tcgen05.mma.cta_group::1.kind::" KIND " [%0], da, db, %3, p;\n\t"                         \
+                     "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %3, p;\n\t"                 \
                      "add.u32 al, %1, 4;\n\tadd.u32 bl, %2, 4;\n\t"                                            \
                      "mov.b64 da, {al, %5};\n\tmov.b64 db, {bl, %5};\n\t"                                      \
-                     "tcgen05.mma.cta_group::1.kind::" KIND " [%0], da, db, %3, p;\n\t"                         \
+                     "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %3, p;\n\t"                 \
                      "add.u32 al, %1, 6;\n\tadd.u32 bl, %2, 6;\n\t"                                            \
                      "mov.b64 da, {al, %5};\n\tmov.b64 db, {bl, %5};\n\t"                                      \
-                     "tcgen05.mma.cta_group::1.kind::" KIND " [%0], da, db, %3, p;\n\t}" ::"r"(d_tmem),          \
+                     "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %3, p;\n\t}" ::"r"(d_tmem),  \
                      "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiK128)                        \
                      : "memory");                                                                              \
     }
-B200Q_MMA_K128(mma_i8_k128, "i8")
-B200Q_MMA_K128(mma_f8_k128, "f8f6f4")
+B200Q_MMA_K128(mma_i8_k128, "1", "i8")
+B200Q_MMA_K128(mma_f8_k128, "1", "f8f6f4")
+B200Q_MMA_K128(mma_i8_pair_k128, "2", "i8")
+B200Q_MMA_K128(mma_f8_pair_k128, "2", "f8f6f4")
 #undef B200Q_MMA_K128
+// Named hardware barrier 4 over 64 threads (the MMA warp and its waiter warp) that also ANDs one
+// predicate per thread: how a waiter tells the issuer "the barriers you need have completed" without
+// the issuer touching shared memory.
+__device__ __forceinline__ bool pair_barrier_and(bool ok) {
+    uint32_t all;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 4, 64, q;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(all)
+                 : "r"(uint32_t(ok))
+                 : "memory");
+    return all != 0;
+}
 // One lane of a converged warp; the same lane every time for the same mask.
 __device__ __forceinline__ bool elect_one() {
     uint32_t elected;

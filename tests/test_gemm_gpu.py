@@ -105,6 +105,25 @@ def test_k_group_gemm(oracle, ctx_factory, mode, fmt, tol, m, n, k, tokens, spli
     assert rel_err(out.float().cpu().numpy(), exact) < tol
 
 
+@pytest.mark.parametrize("mode,fmt,tol", [("group_int8", I8, 1e-2), ("group_fp8", FP8, 2e-2)])
+@pytest.mark.parametrize("m,n,k,residual", [(1300, 1152, 512, False), (2048, 2048, 384, True), (1540, 1168, 256, True)])
+def test_k_group_prefill_kernel(oracle, ctx_factory, mode, fmt, tol, m, n, k, residual):
+    """Enough 128x128 tiles to fill the GPU: the persistent K-group kernel (ragged M and N tiles, several
+    tiles per CTA, optional fp32 residual), against the oracle and against the generic split-K kernel."""
+    ctx = ctx_factory(mode)
+    (xq, sx, wq, sw), (xv, wv) = make_operands(oracle, m, n, k, fmt, 128, 128, seed=m + k, student_t=3.0)
+    skip = synth.activations(m, n, seed=3, outlier_columns=0) if residual else None
+    kw = {"residual_f32": torch.from_numpy(skip).cuda()} if residual else {}
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    ctx.quant_linear((TCGEN05, 128, 128, 1), xv, wv, out, **kw)      # tile count >= 2/3 of the SMs: persistent kernel
+    other = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    ctx.quant_linear((TCGEN05, 64, 128, 1), xv, wv, other, **kw)     # 64-token tiles: the generic kernel
+    _, exact = oracle.quant_linear(xq, sx, wq, sw, fmt, 128, 128, residual_f32=skip)
+    assert ctx.status() == 0
+    assert rel_err(out.float().cpu().numpy(), exact) < tol
+    assert rel_err(out.float().cpu().numpy(), other.float().cpu().numpy().astype(np.float64)) < tol
+
+
 def test_fused_epilogue_chain(oracle, ctx_factory):
     """bias + same-dtype residual + ReLU with the reference's rounding points."""
     ctx = ctx_factory("int8")
