@@ -425,7 +425,11 @@ void launch_quant_linear(LinearPath config, KernelProblem shape, const void *inp
         return;
     }
     const CUtensorMap &map_x = tensor_map(input, shape.rows, shape.reduction, bn, false);
-    const Shape launch = shape_for(bn, grouped, (kb_total + splits - 1) / splits, splits);
+    Shape launch = shape_for(bn, grouped, (kb_total + splits - 1) / splits, splits);
+    // A K-group CTA allocates all 512 columns of tensor memory, so two of them must never share a
+    // multiprocessor (the second allocation would wait for the first CTA, and with split-K clusters
+    // two such waits can form a cycle): ask for more than half of the shared memory.
+    if (grouped) launch.smem = std::max(launch.smem, size_t(120) * 1024);
     args.stages = launch.stages;
     args.tile_region = int(launch.tile_region);
     args.owned_passes = launch.owned_passes;

@@ -139,7 +139,10 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     constexpr bool kIntAcc = kInt && !Grouped; // partial tiles / raw outputs carry int32 bit patterns
     constexpr int kWeightBytes = kBlockChannels * kBlockK, kTokenBytes = BN * kBlockK;
     constexpr int kStageBytes = kWeightBytes + kTokenBytes;
-    constexpr int kAccColumns = Grouped ? 2 * BN : BN;
+    // K-group mode gives every K block its own accumulator for as long as tensor memory lasts (512
+    // columns: 32 buffers at BN=16 ... 4 at BN=128) and reuses them round-robin after that.
+    constexpr int kAccBuffers = Grouped ? (512 / BN > 32 ? 32 : 512 / BN) : 1;
+    constexpr int kAccColumns = Grouped ? kAccBuffers * BN : BN;
     constexpr uint32_t kTmemColumns = kAccColumns <= 32 ? 32 : kAccColumns <= 64 ? 64 : kAccColumns <= 128 ? 128
                                       : kAccColumns <= 256 ? 256 : 512;
     constexpr uint32_t kIdesc = kInt ? ptx::idesc_i8(kBlockChannels, BN) : ptx::idesc_e4m3(kBlockChannels, BN);
@@ -148,7 +151,7 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     constexpr uint32_t kPassBytes = kRowsPerPass * kBlockChannels * 4;
 
     extern __shared__ uint8_t dynamic_smem[];
-    __shared__ alignas(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], acc_full[2], acc_empty[2], x_full;
+    __shared__ alignas(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], acc_full[kAccBuffers], acc_empty[kAccBuffers], x_full;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ float sx_tile[BN]; // per-row activation scales of this token tile
@@ -188,7 +191,7 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
         }
 
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < kAccBuffers; ++b) {
             ptx::mbar_init(ptx::smem_u32(&acc_full[b]), 1);
             ptx::mbar_init(ptx::smem_u32(&acc_empty[b]), kEpilogueThreads / 32);
         }
@@ -255,31 +258,37 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             ok = ok && ptx::mbar_wait(ptx::smem_u32(&x_full), 0u, abort_ptr);
             ok = __all_sync(0xffffffffu, ok);
             if (lane == 0) { B200Q_STAMP(2); B200Q_CLOCK(10); }
-            // Per-row scales: the prefetched stages need no barrier at all any more, so their MMAs go
-            // out back to back (any shared-memory access between MMA issues stalls the issuing warp for
-            // a couple of hundred cycles). Stage i holds K block i here.
+            // The prefetched stages need no barrier at all any more, so their MMAs go out back to back
+            // (any shared-memory access between MMA issues stalls the issuing warp for a couple of
+            // hundred cycles). Stage i holds K block i here; in K-group mode K block i also has
+            // accumulator i to itself while fresh accumulators last.
             int first = 0;
-            if (!Grouped && ok) {
+            if (ok) {
+                const int burst = Grouped ? min(ahead, kAccBuffers) : ahead;
                 ptx::tcgen05_fence_after();
-                for (int it = 0; it < ahead; ++it) {
+                for (int it = 0; it < burst; ++it) {
                     const uint32_t tile = tiles_base + uint32_t(it) * kStageBytes;
+                    const uint32_t d = tmem_base + (Grouped ? uint32_t(it * BN) : 0u);
                     if (ptx::elect_one()) {
-                        if (kInt) ptx::mma_i8_k128(tmem_base, ptx::smem_desc_lo_k128(tile), ptx::smem_desc_lo_k128(tile + kWeightBytes), kIdesc, it > 0);
-                        else ptx::mma_f8_k128(tmem_base, ptx::smem_desc_lo_k128(tile), ptx::smem_desc_lo_k128(tile + kWeightBytes), kIdesc, it > 0);
+                        const uint32_t accumulate = Grouped ? 0u : uint32_t(it > 0);
+                        if (kInt) ptx::mma_i8_k128(d, ptx::smem_desc_lo_k128(tile), ptx::smem_desc_lo_k128(tile + kWeightBytes), kIdesc, accumulate);
+                        else ptx::mma_f8_k128(d, ptx::smem_desc_lo_k128(tile), ptx::smem_desc_lo_k128(tile + kWeightBytes), kIdesc, accumulate);
                         // Only a stage that will be refilled needs to report that its MMAs retired.
                         if (it + a.stages < kb_count) ptx::tcgen05_commit(ptx::smem_u32(&empty_bar[it]));
+                        if (Grouped) ptx::tcgen05_commit(ptx::smem_u32(&acc_full[it]));
                     }
                     __syncwarp();
                 }
-                first = ahead;
+                first = burst;
             }
             if (lane == 0) B200Q_CLOCK(12);
             int stage = first == a.stages ? 0 : first;
             uint32_t phase = first == a.stages ? 1u : 0u;
             // Refilled stages arrive at the rate memory delivers them, one barrier each.
             for (int it = first; it < kb_count && ok; ++it) {
-                const int buffer = Grouped ? (it & 1) : 0;
-                if (Grouped) ok = ptx::mbar_wait(ptx::smem_u32(&acc_empty[buffer]), ((uint32_t(it) >> 1) & 1u) ^ 1u, abort_ptr);
+                const int buffer = Grouped ? it % kAccBuffers : 0;
+                if (Grouped && it >= kAccBuffers) // the epilogue drained this accumulator's previous K block
+                    ok = ptx::mbar_wait(ptx::smem_u32(&acc_empty[buffer]), (uint32_t(it / kAccBuffers) & 1u) ^ 1u, abort_ptr);
                 if (it >= ahead) ok = ok && ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_ptr);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
@@ -405,8 +414,8 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             for (int c = 0; c < kMyChunks * 16; ++c) result[c] = 0.f;
 #pragma unroll 1
             for (int it = 0; it < kb_count && ok; ++it) {
-                const int buffer = it & 1;
-                ok = ptx::mbar_wait(ptx::smem_u32(&acc_full[buffer]), (uint32_t(it) >> 1) & 1u, abort_ptr);
+                const int buffer = it % kAccBuffers;
+                ok = ptx::mbar_wait(ptx::smem_u32(&acc_full[buffer]), uint32_t(it / kAccBuffers) & 1u, abort_ptr);
                 if (!ok) break;
                 ptx::tcgen05_fence_after();
                 const float scale_w = sw_smem[it * kBlockChannels + channel_in_tile];
