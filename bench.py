@@ -313,6 +313,8 @@ def sweep(torch, ops, device, stream):
     for m in (2048, 8192):
         for name, (k, n) in SHAPES.items():
             rows_out.append(dict(measure("fp8", FP8, m, k, n, 0, False, iters=6), config="c3_prefill_fp8", shape=name))
+    for name, (k, n) in SHAPES.items():  # the same prefill shapes in INT8 (the stack's own format)
+        rows_out.append(dict(measure("int8", I8, 8192, k, n, 0, False, iters=6), config="prefill_int8", shape=name))
     for mode, fmt in (("group_int8", I8), ("group_fp8", FP8)):
         for m in (16, 4096):
             rows_out.append(dict(measure(mode, fmt, m, FFN, HIDDEN, 128, False, iters=8), config="c4_group_down", shape="down"))
