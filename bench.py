@@ -1,5 +1,6 @@
 #!/usr/bin/env python
-"""Benchmark of the quantized linear hot path (see DESIGN.md for the definitions).
+"""Benchmark of the quantized linear hot path: one JSON line with the headline metric, the end-to-end
+figure through host buffers, the roofline of the dominant kernel, a CPU baseline and a per-shape sweep.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200q|reference|reference-cpu]
 
