@@ -106,7 +106,8 @@ def test_k_group_gemm(oracle, ctx_factory, mode, fmt, tol, m, n, k, tokens, spli
 
 
 @pytest.mark.parametrize("mode,fmt,tol", [("group_int8", I8, 1e-2), ("group_fp8", FP8, 2e-2)])
-@pytest.mark.parametrize("m,n,k,residual", [(1300, 1152, 512, False), (2048, 2048, 384, True), (1540, 1168, 256, True)])
+@pytest.mark.parametrize("m,n,k,residual", [(1300, 1152, 512, False), (2048, 2048, 384, True), (1540, 1168, 256, True),
+                                            (1300, 1152, 128, True), (1302, 1152, 256, False)])  # one K block; M % 4 != 0 -> generic kernel
 def test_k_group_prefill_kernel(oracle, ctx_factory, mode, fmt, tol, m, n, k, residual):
     """Enough 128x128 tiles to fill the GPU: the persistent K-group kernel (ragged M and N tiles, several
     tiles per CTA, optional fp32 residual), against the oracle and against the generic split-K kernel."""
