@@ -75,11 +75,16 @@ void rotate_row(float *values, int cols) {
 
 // reference: src/ops/kernels/common/activation.cuh:5-27 (the CPU uses libm where the GPU uses
 // fast intrinsics; that difference is why activations are compared with a tolerance).
-float activate(float x, int kind) {
+float activate(float x, int kind, float alpha) {
     switch (kind) {
     case 1: return std::fmax(x, 0.f);
+    case 2: return x >= 0 ? x : x * alpha;
     case 3: return x / (1.f + std::exp(-x));
+    case 4: return .5f * x * (1.f + std::erf(x * .7071067811865475f));
     case 5: return .5f * x * (1.f + std::tanh(.7978845608028654f * (x + .044715f * x * x * x)));
+    case 6: return x * std::tanh(x > 20.f ? x : std::log1p(std::exp(x)));
+    case 7: return std::tanh(x);
+    case 8: return 1.f / (1.f + std::exp(-x));
     default: return x;
     }
 }
@@ -267,7 +272,7 @@ void oracle_quant_linear(const uint8_t *xq, const float *sx, const uint8_t *wq, 
                     }
                     if (ep->activation || ep->output_scale != 1.f) {
                         float scaled = round16(stored * ep->output_scale, output_type);
-                        value = activate(scaled, ep->activation);
+                        value = activate(scaled, ep->activation, ep->alpha);
                         stored = round16(value, output_type);
                     }
                 }

@@ -47,7 +47,9 @@ typedef struct {
     const uint16_t *residual;    /* [m,n], output dtype: reference chain, rounded after the GEMM store */
     const float *residual_f32;   /* [m,n]: synthetic variant, added in fp32 before the single rounding */
     float value_scale, residual_scale, output_scale;
-    int activation;              /* reference ops::Activation: 0 identity, 1 relu, 3 silu, 5 gelu-tanh */
+    int activation;              /* reference ops::Activation: 0 identity, 1 relu, 2 leaky relu, 3 silu, 4 gelu (erf),
+                                    5 gelu-tanh, 6 mish, 7 tanh, 8 sigmoid */
+    float alpha;                 /* negative slope of the leaky relu */
 } oracle_epilogue;
 
 /* Stage 2 / stage 3 GEMM + dequant. Output bf16 (type 0) or f16 (type 5) [m,n]; `exact` (optional)

@@ -17,7 +17,7 @@ BF16, F32, I32, FP8, I8, F16 = 0, 1, 2, 3, 4, 5
 class OracleEpilogue(C.Structure):
     _fields_ = [("bias", C.c_void_p), ("residual", C.c_void_p), ("residual_f32", C.c_void_p),
                 ("value_scale", C.c_float), ("residual_scale", C.c_float), ("output_scale", C.c_float),
-                ("activation", C.c_int)]
+                ("activation", C.c_int), ("alpha", C.c_float)]
 
 
 def _ptr(a):
@@ -87,14 +87,15 @@ class Oracle:
         return acc
 
     def quant_linear(self, xq, sx, wq, sw, fmt, group_x=0, group_w=0, out_type=BF16, bias=None, residual=None,
-                     residual_f32=None, activation=0, value_scale=1.0, residual_scale=1.0, output_scale=1.0, threads=8):
+                     residual_f32=None, activation=0, value_scale=1.0, residual_scale=1.0, output_scale=1.0, alpha=0.1,
+                     threads=8):
         m, k = xq.shape
         n = wq.shape[0]
         out = np.zeros((m, n), dtype=np.uint16)
         exact = np.zeros((m, n), dtype=np.float32)
         keep = [np.ascontiguousarray(a) if a is not None else None for a in (bias, residual, residual_f32)]
         ep = OracleEpilogue(_ptr(keep[0]), _ptr(keep[1]), _ptr(keep[2]), value_scale, residual_scale, output_scale,
-                            activation)
+                            activation, alpha)
         self.lib.oracle_quant_linear(_ptr(np.ascontiguousarray(xq)), _ptr(np.ascontiguousarray(sx)),
                                      _ptr(np.ascontiguousarray(wq)), _ptr(np.ascontiguousarray(sw)), m, n, k, group_x,
                                      group_w, fmt, out_type, _ptr(out), _ptr(exact), C.byref(ep), threads)

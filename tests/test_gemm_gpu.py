@@ -139,6 +139,30 @@ def test_fused_epilogue_chain(oracle, ctx_factory):
     assert np.array_equal(bf16_bits(out), want)
 
 
+@pytest.mark.parametrize("activation", [1, 2, 3, 4, 5, 7, 8])  # relu, leaky relu, silu, gelu, gelu-tanh, tanh, sigmoid
+@pytest.mark.parametrize("m,tokens,splits", [(16, 16, 2), (100, 128, 1)])
+def test_fused_activations(oracle, ctx_factory, activation, m, tokens, splits):
+    """Every activation the fused epilogue accepts, with bias, output scale and the leaky slope, against the
+    oracle. The device uses expf / erff / tanhf where the oracle uses libm, so all but ReLU and leaky ReLU are
+    compared to within two bf16 steps of the value instead of bit for bit."""
+    ctx = ctx_factory("int8")
+    n, k = 384, 512
+    (xq, sx, wq, sw), (xv, wv) = make_operands(oracle, m, n, k, I8, 0, 0, seed=13 + activation)
+    bias16 = oracle.to_bf16(synth.weights(1, n, 5, std=0.5))
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    ctx.quant_linear((TCGEN05, tokens, 128, splits), xv, wv, out, bias=bf16_tensor(bias16), activation=activation,
+                     output_scale=0.5, alpha=0.2)
+    want, _ = oracle.quant_linear(xq, sx, wq, sw, I8, bias=bias16.ravel(), activation=activation, output_scale=0.5,
+                                  alpha=0.2)
+    assert ctx.status() == 0
+    if activation in (1, 2):
+        assert np.array_equal(bf16_bits(out), want)
+    else:
+        expect = (want.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+        got = out.float().cpu().numpy().astype(np.float64)
+        assert np.all(np.abs(got - expect) <= 2.0 ** -7 * np.abs(expect) + 1e-6)
+
+
 def test_rejects_unprepared_and_mismatched(ctx_factory, oracle):
     from breeze_tts_cpp_b200 import B200QError
     ctx = ctx_factory("int8")
