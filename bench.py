@@ -118,9 +118,15 @@ def synth_activations(torch, rows, cols, seed, device, outlier_fraction=0.005):
     return x
 
 
-def synth_weight(torch, n, k, seed, device):
+# The stack has no norm layers, so the two projections that write the residual stream get small weights
+# and the fp32 residual is small: the hidden state then stays finite over all 28 layers (checked each run).
+STACK_STD = {"qkv": 0.02, "o": 0.002, "gate_up": 0.02, "down": 0.002}
+RESIDUAL_SCALE = 0.05
+
+
+def synth_weight(torch, n, k, seed, device, std=0.02):
     g = torch.Generator(device=device).manual_seed(seed)
-    return (torch.randn(n, k, generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    return (torch.randn(n, k, generator=g, device=device, dtype=torch.float32) * std).to(torch.bfloat16)
 
 
 class Stack:
@@ -132,14 +138,14 @@ class Stack:
         for layer in range(layers):
             entry = {}
             for i, (name, (k, n)) in enumerate(SHAPES.items()):
-                w = synth_weight(torch, n, k, SEED + 17 * layer + i, device)
+                w = synth_weight(torch, n, k, SEED + 17 * layer + i, device, STACK_STD[name])
                 view = ops.RowScaledView.empty(n, k, fmt, device=device)
                 ctx.quantize_rows(w, view)
                 entry[name] = view
             self.weights.append(entry)
         torch.cuda.synchronize(device)
         self.x = synth_activations(torch, rows, HIDDEN, SEED - 1, device).to(torch.bfloat16)
-        self.residual = synth_activations(torch, rows, HIDDEN, SEED - 2, device, outlier_fraction=0.0)
+        self.residual = synth_activations(torch, rows, HIDDEN, SEED - 2, device, outlier_fraction=0.0) * RESIDUAL_SCALE
         self.h = torch.empty(rows, HIDDEN, dtype=torch.bfloat16, device=device)
         self.qkv = torch.empty(rows, QKV, dtype=torch.bfloat16, device=device)
         self.gu = torch.empty(rows, 2 * FFN, dtype=torch.bfloat16, device=device)
@@ -243,6 +249,8 @@ def time_steps(args, torch, dist, world, device, stream, stack, graph, gemm_grap
         for _ in range(max(1, args.warmup // 2)):
             e2e_step()
     ms_e2e = timed(e2e_step, args.steps)
+    if not bool(torch.isfinite(host_out.float()).all()):
+        raise SystemExit("bench: the step output read back to the host is not finite")
     with torch.cuda.stream(stream):
         for _ in range(max(1, args.warmup // 2)):
             gemm_graph.replay()
@@ -370,7 +378,7 @@ def run_reference(args, torch, dist, rank, world, device):
         # the reference quantizes its own weights too: overwrite with its kernel so nothing of ours is on the path
         for layer_index, layer in enumerate(stack.weights):
             for i, (name, (k, n)) in enumerate(SHAPES.items()):
-                w = synth_weight(torch, n, k, SEED + 17 * layer_index + i, device)
+                w = synth_weight(torch, n, k, SEED + 17 * layer_index + i, device, STACK_STD[name])
                 rc = lib.ttsref_row_quantize(w.data_ptr(), n, k, 0, BF16, layer[name].values.data_ptr(),
                                              layer[name].scales.data_ptr(), I8, 0, 0, sp)
                 assert rc == 0, lib.ttsref_last_error()
