@@ -1,16 +1,21 @@
 #!/usr/bin/env python
 """Benchmark of the quantized linear hot path: one JSON line with the headline metric, the end-to-end
-figure through host buffers, the roofline of the dominant kernel, a CPU baseline and a per-shape sweep.
+figure through host buffers, the roofline of the dominant kernel, a CPU baseline and one row per
+benchmark configuration.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200q|reference|reference-cpu]
+    python bench.py --case <qkv|o|gate_up|down> <rows> [mode] [launches]     (one small case for a profiler)
 
 Workload (`config.workload`): the quantized linears of a synthetic 28-layer decoder stack
 (hidden 2048, fused QKV 4096, O 2048, fused gate+up 12288, down 6144->2048; INT8 W8A8 with
 per-channel weight scales and dynamic per-token activation scales), 64 concurrent decode streams
 sharded data-parallel over the GPUs (64/N rows per GPU), weights replicated. One step = one decode
-step: for every layer quantize -> QKV GEMM, quantize -> O GEMM (+fp32 residual), quantize ->
-gate/up GEMM, SiLU-gate+quantize -> down GEMM (+fp32 residual); 224 kernel launches replayed as one
-CUDA graph. A step streams 1.41 GB of distinct weights, far more than the 126 MB L2.
+step through the chain the reference decoder runs (src/layers/transformer/decoder.h:241-293): per
+layer  residual-add + RMSNorm + quantize -> QKV GEMM -> row quantize (stands for the attention
+output) -> O GEMM -> residual-add + RMSNorm + quantize -> gate/up GEMM -> SiLU-gate + quantize ->
+down GEMM;  8 launches per layer, 224 per step, replayed as one CUDA graph. A step streams 1.41 GB
+of distinct weights, far more than the 126 MB L2. Both arms (`--impl b200q`, `--impl reference`) run
+the same chain; the reference arm uses only the reference's own kernels and plain torch tensors.
 
 Prints ONE JSON line on rank 0.
 """
@@ -32,6 +37,14 @@ sys.path.insert(0, str(ROOT))
 HIDDEN, QKV, FFN, LAYERS, STREAMS = 2048, 4096, 6144, 28, 64
 SHAPES = {"qkv": (HIDDEN, QKV), "o": (HIDDEN, HIDDEN), "gate_up": (HIDDEN, 2 * FFN), "down": (FFN, HIDDEN)}  # name: (K, N)
 SEED = 0x5EED
+EPSILON = 1e-6
+BF16, FP8, I8 = 0, 3, 4  # tts::Type codes
+NOMINAL_HBM_GBS, NOMINAL_TENSOR_TOPS = 8000.0, 4500.0
+
+# DRAM bytes (read + written) of one GEMM launch at M=64, from single-launch ncu captures of each of
+# the four layer shapes (dram__bytes_read.sum + dram__bytes_write.sum). Other row counts scale them
+# by the algorithmic bytes, which is what the traffic follows (weights dominate both).
+NCU_DRAM_BYTES_M64 = {"qkv": None, "o": None, "gate_up": 25_410_000 + 1_572_864, "down": None}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -45,10 +58,7 @@ def linear_bytes(m, k, n, residual=False, group=0, quantize=True):
 
 
 def step_bytes(m, gemm_only=False):
-    total = 0
-    for name, (k, n) in SHAPES.items():
-        total += linear_bytes(m, k, n, residual=name in ("o", "down"), quantize=not gemm_only)
-    return total * LAYERS
+    return LAYERS * sum(linear_bytes(m, k, n, quantize=not gemm_only) for k, n in SHAPES.values())
 
 
 def step_ops(m):
@@ -65,7 +75,7 @@ def measured_peaks():
 
 # ------------------------------------------------------------------------------------------------
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs (queries only)."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -109,19 +119,16 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------
-def synth_activations(torch, rows, cols, seed, device, outlier_fraction=0.005):
+def synth_activations(torch, rows, cols, seed, device, outlier_fraction=0.005, student_t=False):
     g = torch.Generator(device=device).manual_seed(seed)
     x = torch.randn(rows, cols, generator=g, device=device, dtype=torch.float32)
-    count = max(1, round(cols * outlier_fraction))
-    columns = torch.randperm(cols, generator=g, device=device)[:count]
-    x[:, columns] *= 20.0
+    if student_t:  # Student-t, 3 degrees of freedom
+        x = x / (torch.randn(3, rows, cols, generator=g, device=device).pow(2).sum(0) / 3).sqrt()
+    count = max(1, round(cols * outlier_fraction)) if outlier_fraction else 0
+    if count:
+        columns = torch.randperm(cols, generator=g, device=device)[:count]
+        x[:, columns] *= 20.0
     return x
-
-
-# The stack has no norm layers, so the two projections that write the residual stream get small weights
-# and the fp32 residual is small: the hidden state then stays finite over all 28 layers (checked each run).
-STACK_STD = {"qkv": 0.02, "o": 0.002, "gate_up": 0.02, "down": 0.002}
-RESIDUAL_SCALE = 0.05
 
 
 def synth_weight(torch, n, k, seed, device, std=0.02):
@@ -129,82 +136,200 @@ def synth_weight(torch, n, k, seed, device, std=0.02):
     return (torch.randn(n, k, generator=g, device=device, dtype=torch.float32) * std).to(torch.bfloat16)
 
 
-class Stack:
-    """Weights (quantized once at load, like the reference's Weights::quantized) and activation buffers."""
+class Quantized:
+    """One-byte values [rows, K] + fp32 scales, as plain torch tensors (both arms read these)."""
 
-    def __init__(self, torch, ops, ctx, rows, device, fmt, layers=LAYERS):
+    def __init__(self, torch, rows, cols, device, group=0):
+        self.values = torch.empty(rows, cols, dtype=torch.uint8, device=device)
+        self.scales = torch.empty(((cols + group - 1) // group, rows) if group else (rows, 1), dtype=torch.float32, device=device)
+        self.rows, self.cols, self.group = rows, cols, group
+
+
+class Stack:
+    """Weights (quantized once at load by the arm's own quantizer, like the reference's Weights::quantized),
+    norm weights and activation buffers of the synthetic decoder."""
+
+    def __init__(self, torch, arm, rows, device, layers=LAYERS):
         self.rows, self.layers = rows, layers
         self.weights = []
         for layer in range(layers):
             entry = {}
             for i, (name, (k, n)) in enumerate(SHAPES.items()):
-                w = synth_weight(torch, n, k, SEED + 17 * layer + i, device, STACK_STD[name])
-                view = ops.RowScaledView.empty(n, k, fmt, device=device)
-                ctx.quantize_rows(w, view)
-                entry[name] = view
+                w = synth_weight(torch, n, k, SEED + 17 * layer + i, device)
+                entry[name] = Quantized(torch, n, k, device)
+                arm.quantize(w, entry[name])
+            g = torch.Generator(device=device).manual_seed(SEED + 1000 + layer)
+            for name in ("pre", "post"):
+                entry[name] = (1.0 + 0.1 * torch.randn(1, HIDDEN, generator=g, device=device)).to(torch.bfloat16)
             self.weights.append(entry)
         torch.cuda.synchronize(device)
-        self.x = synth_activations(torch, rows, HIDDEN, SEED - 1, device).to(torch.bfloat16)
-        self.residual = synth_activations(torch, rows, HIDDEN, SEED - 2, device, outlier_fraction=0.0) * RESIDUAL_SCALE
-        self.h = torch.empty(rows, HIDDEN, dtype=torch.bfloat16, device=device)
+        self.x0 = synth_activations(torch, rows, HIDDEN, SEED - 1, device).to(torch.bfloat16)
+        self.x = torch.empty_like(self.x0)                                            # residual stream
+        self.u = torch.zeros(rows, HIDDEN, dtype=torch.bfloat16, device=device)      # branch output (O / down)
         self.qkv = torch.empty(rows, QKV, dtype=torch.bfloat16, device=device)
         self.gu = torch.empty(rows, 2 * FFN, dtype=torch.bfloat16, device=device)
-        self.q_hidden = ops.RowScaledView.empty(rows, HIDDEN, fmt, device=device)
-        self.q_ffn = ops.RowScaledView.empty(rows, FFN, fmt, device=device)
+        self.q_hidden = Quantized(torch, rows, HIDDEN, device)
+        self.q_ffn = Quantized(torch, rows, FFN, device)
 
 
-def run_b200q(args, torch, dist, rank, world, device):
-    from breeze_tts_cpp_b200 import I8, ops
+def decode_step(arm, stack, gemm_only=False):
+    """The chain both arms run; `arm` supplies the kernels."""
+    s = stack
+    for index, layer in enumerate(s.weights):
+        if not gemm_only:
+            arm.norm(s.x, s.u if index else None, layer["pre"], s.q_hidden)
+        arm.gemm("qkv", s.q_hidden, layer["qkv"], s.qkv)
+        if not gemm_only:
+            arm.quantize(s.qkv[:, :HIDDEN], s.q_hidden)
+        arm.gemm("o", s.q_hidden, layer["o"], s.u)
+        if not gemm_only:
+            arm.norm(s.x, s.u, layer["post"], s.q_hidden)
+        arm.gemm("gate_up", s.q_hidden, layer["gate_up"], s.gu)
+        if not gemm_only:
+            arm.gated(s.gu, s.q_ffn)
+        arm.gemm("down", s.q_ffn, layer["down"], s.u)
+
+
+LAUNCHES_PER_STEP = LAYERS * 8
+
+
+# ------------------------------------------------------------------------------------------------ arms
+class B200QArm:
+    """This library through its C ABI (ctypes binding in breeze_tts_cpp_b200/ops.py)."""
+
+    def __init__(self, torch, device, stream, rows):
+        from breeze_tts_cpp_b200 import ops
+        self.ops, self.torch = ops, torch
+        self.ctx = ops.Context("int8", device=device.index, stream=stream, workspace_bytes=8 << 20)
+        self.rows = rows
+
+    def view(self, q):
+        return self.ops.RowScaledView(q.values, q.scales, I8, q.group, q.group)
+
+    def prepare(self, stack):
+        for layer in stack.weights:
+            for name, (k, n) in SHAPES.items():
+                self.ctx.prepare_quantized(self.rows, n, k, weight=self.view(layer[name]))
+        self.ctx.seal()
+
+    def quantize(self, x, q):
+        self.ctx.quantize_rows(x, self.view(q))
+
+    def norm(self, x, update, weight, q):
+        self.ctx.quantized_norm(x, update, weight, self.view(q), EPSILON)
+
+    def gated(self, gu, q):
+        self.ctx.quantized_gated(gu, self.view(q), 0)
+
+    def gemm(self, name, q, w, out):
+        self.ctx.matmul(self.view(q), self.view(w), out)
+
+    def status(self):
+        return self.ctx.status()
+
+
+class ReferenceArm:
+    """The reference's own CUDA kernels (built from its sources into oracle/_ref/libttsref.so) over plain torch
+    tensors; nothing of this library is imported. The reference has no CPU implementation of this path; its stock
+    code path on sm_100 is the CUTLASS SM80 GEMM / scalar GEMV chosen per shape, here by timing every candidate
+    its planner enumerates."""
+
+    def __init__(self, torch, device, stream, rows, lib):
+        self.torch, self.lib, self.rows = torch, lib, rows
+        self.sp = C.c_void_p(stream.cuda_stream)
+        self.stream = stream
+        self.workspace = torch.zeros(8 << 20, dtype=torch.uint8, device=device)
+        self.sms = torch.cuda.get_device_properties(device).multi_processor_count
+        self.best = {}
+
+    def check(self, rc):
+        if rc != 0:
+            raise RuntimeError(self.lib.ttsref_last_error().decode())
+
+    def quantize(self, x, q):
+        stride = x.stride(0) if x.stride(0) != x.shape[1] else 0
+        self.check(self.lib.ttsref_row_quantize(x.data_ptr(), x.shape[0], x.shape[1], stride, BF16, q.values.data_ptr(),
+                                                q.scales.data_ptr(), I8, 0, 0, self.sp))
+
+    def norm(self, x, update, weight, q):
+        self.check(self.lib.ttsref_quantized_norm(x.data_ptr(), update.data_ptr() if update is not None else None,
+                                                  weight.data_ptr(), None, x.shape[0], x.shape[1], BF16, q.values.data_ptr(),
+                                                  q.scales.data_ptr(), I8, 0, 0, EPSILON, 0, self.sp))
+
+    def gated(self, gu, q):
+        self.check(self.lib.ttsref_quantized_gated(gu.data_ptr(), gu.shape[0], gu.shape[1] // 2, BF16, q.values.data_ptr(),
+                                                   q.scales.data_ptr(), I8, 0, 0, 0, self.sms, 1, self.sp))
+
+    def gemm_path(self, path, q, w, out):
+        self.check(self.lib.ttsref_quant_linear(path[0], path[1], path[2], path[3], q.rows, w.rows, w.cols, 0, 0,
+                                                q.values.data_ptr(), q.scales.data_ptr(), w.values.data_ptr(),
+                                                w.scales.data_ptr(), out.data_ptr(), self.workspace.data_ptr(),
+                                                self.workspace.numel(), self.sp, I8, BF16))
+
+    def gemm(self, name, q, w, out):
+        self.gemm_path(self.best[name], q, w, out)
+
+    def prepare(self, stack):
+        """Best of the candidates the reference planner enumerates, per shape (a stronger baseline than its cost
+        model's pick), timed over eight layers' distinct weights."""
+        torch = self.torch
+        buffers = {"qkv": stack.qkv, "o": stack.u, "gate_up": stack.gu, "down": stack.u}
+        for name, (k, n) in SHAPES.items():
+            cand = (C.c_int * (4 * 256))()
+            count = self.lib.ttsref_candidates(self.rows, n, k, 0, 0, I8, 48 << 10, 8 << 20, cand, 256)
+            q = stack.q_hidden if k == HIDDEN else stack.q_ffn
+            q.values.random_(0, 255)
+            q.scales.fill_(0.01)
+            timings = []
+            for c in range(min(count, 256)):
+                path = tuple(cand[4 * c:4 * c + 4])
+                try:
+                    ws = [stack.weights[i][name] for i in range(min(LAYERS, 8))]
+                    for w in ws:
+                        self.gemm_path(path, q, w, buffers[name])
+                    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    start.record(self.stream)
+                    for _ in range(2):
+                        for w in ws:
+                            self.gemm_path(path, q, w, buffers[name])
+                    stop.record(self.stream)
+                    stop.synchronize()
+                    timings.append((start.elapsed_time(stop), path))
+                except RuntimeError:
+                    continue
+            self.best[name] = min(timings)[1]
+
+    def status(self):
+        return 0
+
+
+# ------------------------------------------------------------------------------------------------
+def run_chain(args, torch, dist, rank, world, device, arm_factory):
     rows = STREAMS // world
     stream = torch.cuda.Stream(device=device)
     with torch.cuda.stream(stream):
-        ctx = ops.Context("int8", device=device.index, stream=stream, workspace_bytes=8 << 20)
-        stack = Stack(torch, ops, ctx, rows, device, I8)
-        for k, n in SHAPES.values():
-            ctx.prepare_quantized(rows, n, k)
-        ctx.seal()
-
-        def decode_step(gemm_only=False):
-            h = stack.h
-            for layer in stack.weights:
-                if not gemm_only:
-                    ctx.quantize_rows(h, stack.q_hidden)
-                ctx.matmul(stack.q_hidden, layer["qkv"], stack.qkv)
-                if not gemm_only:
-                    ctx.quantize_rows(stack.qkv[:, :HIDDEN], stack.q_hidden)
-                ctx.matmul(stack.q_hidden, layer["o"], h, residual_f32=stack.residual)
-                if not gemm_only:
-                    ctx.quantize_rows(h, stack.q_hidden)
-                ctx.matmul(stack.q_hidden, layer["gate_up"], stack.gu)
-                if not gemm_only:
-                    ctx.quantized_gated(stack.gu, stack.q_ffn, 0)
-                ctx.matmul(stack.q_ffn, layer["down"], h, residual_f32=stack.residual)
-
-        stack.h.copy_(stack.x)
-        decode_step()  # eager once: plans, tensor maps, lazy module loading
+        arm = arm_factory(stream, rows)
+        stack = Stack(torch, arm, rows, device)
+        arm.prepare(stack)
+        stack.x.copy_(stack.x0)
+        decode_step(arm, stack)  # eager once: lazy module loading, plans
         stream.synchronize()
-        assert ctx.status() == 0, "device status word set"
+        assert arm.status() == 0, "device status word set"
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
-            decode_step()
+            decode_step(arm, stack)
         gemm_graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(gemm_graph, stream=stream):
-            decode_step(gemm_only=True)
-
-    launches_per_step = LAYERS * 8
+            decode_step(arm, stack, gemm_only=True)
     result = time_steps(args, torch, dist, world, device, stream, stack, graph, gemm_graph)
-    assert ctx.status() == 0, "device status word set during the timed region"
-    result["gpu_launches"] = launches_per_step * args.steps
-    extras = {}
-    if rank == 0 and world == 1 and not args.no_sweep:
-        extras = sweep(torch, ops, device, stream)
-    return result, extras
+    assert arm.status() == 0, "device status word set during the timed region"
+    return arm, stream, result
 
 
 def time_steps(args, torch, dist, world, device, stream, stack, graph, gemm_graph):
     """value: K graph replays with inputs resident; e2e: per step H2D of the step input, replay, D2H of the
     step result, stream sync; roofline: K replays of the GEMM launches alone."""
-    host_x = stack.x.cpu().pin_memory()
+    host_x = stack.x0.cpu().pin_memory()
     host_out = torch.empty(stack.rows, HIDDEN, dtype=torch.bfloat16).pin_memory()
 
     def barrier():
@@ -222,21 +347,16 @@ def time_steps(args, torch, dist, world, device, stream, stack, graph, gemm_grap
             stop.record(stream)
         stop.synchronize()
         barrier()
-        ms = start.elapsed_time(stop)
-        if world > 1:
-            t = torch.tensor([ms], device=device, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+        return start.elapsed_time(stop)
 
     def resident_step():
-        stack.h.copy_(stack.x, non_blocking=True)  # device-to-device reset of the step input
+        stack.x.copy_(stack.x0, non_blocking=True)  # device-to-device reset of the residual stream
         graph.replay()
 
     def e2e_step():
-        stack.h.copy_(host_x, non_blocking=True)
+        stack.x.copy_(host_x, non_blocking=True)
         graph.replay()
-        host_out.copy_(stack.h, non_blocking=True)
+        host_out.copy_(stack.u, non_blocking=True)
         stream.synchronize()
 
     with torch.cuda.stream(stream):
@@ -249,8 +369,8 @@ def time_steps(args, torch, dist, world, device, stream, stack, graph, gemm_grap
         for _ in range(max(1, args.warmup // 2)):
             e2e_step()
     ms_e2e = timed(e2e_step, args.steps)
-    if not bool(torch.isfinite(host_out.float()).all()):
-        raise SystemExit("bench: the step output read back to the host is not finite")
+    if not bool(torch.isfinite(host_out.float()).all()) or float(host_out.float().abs().max()) == 0.0:
+        raise SystemExit("bench: the step output read back to the host is not a finite, nonzero tensor")
     with torch.cuda.stream(stream):
         for _ in range(max(1, args.warmup // 2)):
             gemm_graph.replay()
@@ -259,29 +379,108 @@ def time_steps(args, torch, dist, world, device, stream, stack, graph, gemm_grap
             "h2d": host_x.numel() * 2, "d2h": host_out.numel() * 2}
 
 
-def sweep(torch, ops, device, stream):
-    """Per-shape numbers for the other configurations (decode sweep, FP8 prefill, K-group down projection),
-    each rotated over enough distinct weight copies to exceed L2. `us`/`gbs`/`tops` time quantize + GEMM,
-    `gemm_*` the GEMM launches alone. Reported beside the headline, not as it."""
-    from breeze_tts_cpp_b200 import FP8, I8
-    peaks = measured_peaks()
+# ------------------------------------------------------------------------------------------------ per-configuration rows
+def library_tensor_peaks(torch, device):
+    """Dense 8-bit GEMM rate of the vendor library at 8192^3 on this GPU (best of 10): the measured denominator of
+    the prefill rows. A library peak, not a reference path."""
+    out = {}
+    n = 8192
+    ops = 2.0 * n ** 3
+
+    def best(fn):
+        fn()
+        torch.cuda.synchronize(device)
+        times = []
+        for _ in range(10):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            stop.record()
+            stop.synchronize()
+            times.append(start.elapsed_time(stop))
+        return ops / (min(times) * 1e-3) / 1e12
+
+    try:
+        a = torch.randint(-100, 100, (n, n), dtype=torch.int8, device=device)
+        b = torch.randint(-100, 100, (n, n), dtype=torch.int8, device=device).t()
+        out["int8_tops"] = round(best(lambda: torch._int_mm(a, b)), 1)
+    except Exception as error:  # noqa: BLE001
+        out["int8_tops"], out["int8_error"] = None, str(error)[:80]
+    try:
+        a = torch.randn(n, n, device=device).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=device).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=device)
+        out["fp8_tflops"] = round(best(lambda: torch._scaled_mm(a, b, one, one, out_dtype=torch.bfloat16)), 1)
+    except Exception as error:  # noqa: BLE001
+        out["fp8_tflops"], out["fp8_error"] = None, str(error)[:80]
+    out["how"] = "torch._int_mm / torch._scaled_mm (cuBLASLt) 8192^3, best of 10, CUDA events: library peak, not a reference path"
+    return out
+
+
+def check_output(torch, fmt, group, xq, wq, out, residual):
+    """Plain PyTorch restatement of the arithmetic on a slice of the output (a checker, never the product): INT8
+    per-row must match bit for bit (exact INT32 sums, the same fp32 rounding chain), the other modes within
+    2e-2 (FP8) / 1e-2 (INT8 K-group) relative with floor 1e-2 * rms."""
+    m, n = out.shape
+    g = torch.Generator(device="cpu").manual_seed(1)
+    channels = torch.unique(torch.cat([torch.arange(0, n, 128), torch.arange(127, n, 128), torch.randint(0, n, (64,), generator=g)])).to(out.device)
+    rows = torch.unique(torch.cat([torch.arange(0, m, 128), torch.arange(min(m, 127), m, 128), torch.randint(0, m, (64,), generator=g)])).to(out.device)
+    got = out[rows][:, channels]
+    skip = residual[rows][:, channels] if residual is not None else None
+    xs, ws = xq.values[rows], wq.values[channels]
+    if fmt == I8 and not group:
+        pad = max(32, -(-rows.numel() // 8) * 8)
+        a = torch.zeros(pad, xs.shape[1], dtype=torch.int8, device=out.device)
+        a[:rows.numel()] = xs.view(torch.int8)
+        pad_n = -(-channels.numel() // 8) * 8
+        b = torch.zeros(pad_n, ws.shape[1], dtype=torch.int8, device=out.device)
+        b[:channels.numel()] = ws.view(torch.int8)
+        acc = torch._int_mm(a, b.t())[:rows.numel(), :channels.numel()]
+        want = (acc.float() * xq.scales.reshape(-1, 1)[rows]) * wq.scales.reshape(1, -1)[:, channels]
+        if skip is not None:
+            want = want + skip
+        return bool(torch.equal(want.to(torch.bfloat16).view(torch.int16), got.contiguous().view(torch.int16)))
+    decode = (lambda t: t.view(torch.int8).double()) if fmt == I8 else (lambda t: t.view(torch.float8_e4m3fn).double())
+    x, w = decode(xs), decode(ws)
+    if group:
+        want = torch.zeros(rows.numel(), channels.numel(), dtype=torch.float64, device=out.device)
+        for block in range(x.shape[1] // group):
+            part = x[:, block * group:(block + 1) * group] @ w[:, block * group:(block + 1) * group].T
+            want += part * xq.scales[block][rows].double().reshape(-1, 1) * wq.scales[block][channels].double().reshape(1, -1)
+    else:
+        want = (x @ w.T) * xq.scales.reshape(-1, 1)[rows].double() * wq.scales.reshape(1, -1)[:, channels].double()
+    if skip is not None:
+        want = want + skip.double()
+    floor = 1e-2 * want.pow(2).mean().sqrt() + 1e-30
+    error = float(((got.double() - want).abs() / torch.maximum(want.abs(), floor)).max())
+    return error < (2e-2 if fmt == FP8 else 1e-2)
+
+
+def config_rows(torch, device, stream, peaks, tensor_peaks):
+    """One row per shape of BASELINE configurations 1-4, each rotated over enough distinct weight copies to exceed
+    L2. `us` times quantize + GEMM, `gemm_us` the GEMM launch alone (CUDA-graph replays); decode rows are held
+    against the HBM roofline, prefill rows against the dense 8-bit tensor rate."""
+    from breeze_tts_cpp_b200 import ops
     rows_out = []
 
-    def measure(mode, fmt, m, k, n, group, residual, iters=20):
+    def measure(config, shape, mode, fmt, m, k, n, group, residual, bound, iters=20, student_t=False):
         ctx = ops.Context(mode, device=device.index, stream=stream, workspace_bytes=8 << 20)
         copies = max(2, min(24, (300 << 20) // (n * k)))
-        rot = 128 if group else 0
         with torch.cuda.stream(stream):
             ws = []
             for c in range(copies):
                 w = synth_weight(torch, n, k, SEED + c, device)
-                ws.append(ctx.quantize_rows(w, ops.RowScaledView.empty(n, k, fmt, group, rot, device=device)))
-            x = synth_activations(torch, m, k, SEED, device).to(torch.bfloat16)
-            xq = ops.RowScaledView.empty(m, k, fmt, group, rot, device=device)
+                ws.append(ctx.quantize_rows(w, ops.RowScaledView.empty(n, k, fmt, group, group, device=device)))
+            x = synth_activations(torch, m, k, SEED, device, student_t=student_t).to(torch.bfloat16)
+            xq = ops.RowScaledView.empty(m, k, fmt, group, group, device=device)
             out = torch.empty(m, n, dtype=torch.bfloat16, device=device)
             res = torch.randn(m, n, device=device) if residual else None
             path = ctx.prepare_quantized(m, n, k)
             kw = {"residual_f32": res} if residual else {}
+            ctx.quantize_rows(x, xq)
+            ctx.matmul(xq, ws[-1], out, **kw)
+            stream.synchronize()
+            checked = check_output(torch, fmt, group, xq, ws[-1], out, res)
 
             def body(gemm_only):
                 for w in ws:
@@ -311,23 +510,37 @@ def sweep(torch, ops, device, stream):
         ctx.close()
         nbytes = linear_bytes(m, k, n, residual, group)
         gemm_bytes = linear_bytes(m, k, n, residual, group, quantize=False)
-        return {"mode": mode, "m": m, "k": k, "n": n, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
-                "tops": round(2.0 * m * n * k / us / 1e6, 1), "hbm_frac_measured": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 3),
-                "gemm_us": round(gemm_us, 2), "gemm_gbs": round(gemm_bytes / gemm_us / 1e3, 1),
-                "gemm_tops": round(2.0 * m * n * k / gemm_us / 1e6, 1), "path": list(path), "status": status}
+        ops_count = 2.0 * m * n * k
+        row = {"config": config, "shape": shape, "mode": mode, "m": m, "k": k, "n": n, "bound": bound,
+               "algorithmic_bytes": nbytes, "ops": ops_count, "us": round(us, 2), "gemm_us": round(gemm_us, 2),
+               "path": list(path), "checked": bool(checked and status == 0)}
+        if bound == "hbm":
+            row.update(gbs=round(nbytes / us / 1e3, 1), gemm_gbs=round(gemm_bytes / gemm_us / 1e3, 1),
+                       frac_of_measured=round(nbytes / us / 1e3 / peaks["hbm_gbs"], 3),
+                       gemm_frac_of_measured=round(gemm_bytes / gemm_us / 1e3 / peaks["hbm_gbs"], 3),
+                       gemm_frac_of_nominal=round(gemm_bytes / gemm_us / 1e3 / NOMINAL_HBM_GBS, 3))
+        else:
+            library = tensor_peaks.get("fp8_tflops" if fmt == FP8 else "int8_tops")
+            tops, gemm_tops = ops_count / us / 1e6, ops_count / gemm_us / 1e6
+            row.update(tops=round(tops, 1), gemm_tops=round(gemm_tops, 1),
+                       frac_of_measured=round(tops / library, 3) if library else None,
+                       gemm_frac_of_measured=round(gemm_tops / library, 3) if library else None,
+                       gemm_frac_of_nominal=round(gemm_tops / NOMINAL_TENSOR_TOPS, 3))
+        return row
 
+    rows_out.append(measure("c1", "o", "int8", I8, 16, HIDDEN, HIDDEN, 0, False, "hbm"))
     for m in (1, 4, 16, 64):
         for name, (k, n) in SHAPES.items():
-            rows_out.append(dict(measure("int8", I8, m, k, n, 0, True), config="c2_decode", shape=name))
+            rows_out.append(measure("c2", name, "int8", I8, m, k, n, 0, True, "hbm"))
     for m in (2048, 8192):
         for name, (k, n) in SHAPES.items():
-            rows_out.append(dict(measure("fp8", FP8, m, k, n, 0, False, iters=6), config="c3_prefill_fp8", shape=name))
+            rows_out.append(measure("c3", name, "fp8", FP8, m, k, n, 0, False, "tensor", iters=6))
     for name, (k, n) in SHAPES.items():  # the same prefill shapes in INT8 (the stack's own format)
-        rows_out.append(dict(measure("int8", I8, 8192, k, n, 0, False, iters=6), config="prefill_int8", shape=name))
+        rows_out.append(measure("c3_int8", name, "int8", I8, 8192, k, n, 0, False, "tensor", iters=6))
     for mode, fmt in (("group_int8", I8), ("group_fp8", FP8)):
-        for m in (16, 4096):
-            rows_out.append(dict(measure(mode, fmt, m, FFN, HIDDEN, 128, False, iters=8), config="c4_group_down", shape="down"))
-    return {"sweep": rows_out}
+        rows_out.append(measure("c4", "down", mode, fmt, 16, FFN, HIDDEN, 128, False, "hbm", iters=8, student_t=True))
+        rows_out.append(measure("c4", "down", mode, fmt, 4096, FFN, HIDDEN, 128, False, "tensor", iters=8, student_t=True))
+    return rows_out
 
 
 # ------------------------------------------------------------------------------------------------
@@ -345,122 +558,15 @@ def cpu_baseline(rows, max_seconds=20.0):
         wq = rng.integers(-127, 128, (n, k), dtype=np.int8).view(np.uint8)
         sw = np.full(n, 1e-3, dtype=np.float32)
         out = np.zeros((rows, n), dtype=np.uint16)
-        residual = rng.standard_normal((rows, n)).astype(np.float32) if name in ("o", "down") else None
         seconds = oracle.lib.oracle_time_linear(x16.ctypes.data, wq.ctypes.data, sw.ctypes.data, rows, n, k, n, 4, 0, 0,
-                                                out.ctypes.data, residual.ctypes.data if residual is not None else None,
-                                                threads)
+                                                out.ctypes.data, None, threads)
         total_s += seconds
-        total_bytes += linear_bytes(rows, k, n, residual is not None)
+        total_bytes += linear_bytes(rows, k, n)
         done.append(name)
         if total_s > max_seconds:
             break
     return {"value": round(total_bytes / total_s / 1e9, 4), "unit": "GB/s", "cores": threads, "kind": "port",
             "sample": f"one decoder layer ({'+'.join(done)}) at M={rows}: quantize+GEMM+dequant in {total_s:.2f} s"}
-
-
-# ------------------------------------------------------------------------------------------------
-def run_reference(args, torch, dist, rank, world, device):
-    """The reference's own CUDA kernels (built from its sources into oracle/_ref/libttsref.so) on the same chain.
-    The reference has no CPU implementation of this path; its stock code path on sm_100 is the CUTLASS SM80
-    GEMM / scalar GEMV chosen per shape, here by timing every candidate its planner enumerates."""
-    from tests import oracle_binding
-    lib = oracle_binding.load_reference()
-    if lib is None:
-        return None
-    from breeze_tts_cpp_b200 import I8, ops
-    rows = STREAMS // world
-    BF16 = 0
-    stream = torch.cuda.Stream(device=device)
-    sp = C.c_void_p(stream.cuda_stream)
-    with torch.cuda.stream(stream):
-        ctx = ops.Context("int8", device=device.index, stream=stream)  # only to own buffers' helper types
-        stack = Stack(torch, ops, ctx, rows, device, I8)
-        # the reference quantizes its own weights too: overwrite with its kernel so nothing of ours is on the path
-        for layer_index, layer in enumerate(stack.weights):
-            for i, (name, (k, n)) in enumerate(SHAPES.items()):
-                w = synth_weight(torch, n, k, SEED + 17 * layer_index + i, device, STACK_STD[name])
-                rc = lib.ttsref_row_quantize(w.data_ptr(), n, k, 0, BF16, layer[name].values.data_ptr(),
-                                             layer[name].scales.data_ptr(), I8, 0, 0, sp)
-                assert rc == 0, lib.ttsref_last_error()
-        ctx.close()
-        workspace = torch.zeros(8 << 20, dtype=torch.uint8, device=device)
-        props = torch.cuda.get_device_properties(device)
-
-        def gemm(path, xq, w, out, k, n):
-            rc = lib.ttsref_quant_linear(path[0], path[1], path[2], path[3], rows, n, k, 0, 0, xq.values.data_ptr(),
-                                         xq.scales.data_ptr(), w.values.data_ptr(), w.scales.data_ptr(), out.data_ptr(),
-                                         workspace.data_ptr(), workspace.numel(), sp, I8, BF16)
-            if rc != 0:
-                raise RuntimeError(lib.ttsref_last_error().decode())
-
-        def quantize(x, q):
-            stride = x.stride(0) if x.stride(0) != x.shape[1] else 0
-            rc = lib.ttsref_row_quantize(x.data_ptr(), x.shape[0], x.shape[1], stride, BF16, q.values.data_ptr(),
-                                         q.scales.data_ptr(), I8, 0, 0, sp)
-            assert rc == 0, lib.ttsref_last_error()
-
-        # best-of-candidates per shape (a stronger baseline than the cost model's pick)
-        best = {}
-        buffers = {"qkv": stack.qkv, "o": stack.h, "gate_up": stack.gu, "down": stack.h}
-        for name, (k, n) in SHAPES.items():
-            cand = (C.c_int * (4 * 256))()
-            count = lib.ttsref_candidates(rows, n, k, 0, 0, I8, 48 << 10, 8 << 20, cand, 256)
-            xq = stack.q_hidden if k == HIDDEN else stack.q_ffn
-            xq.values.random_(0, 255)
-            xq.scales.fill_(0.01)
-            timings = []
-            for c in range(min(count, 256)):
-                path = tuple(cand[4 * c:4 * c + 4])
-                try:
-                    ws = [stack.weights[i][name] for i in range(min(LAYERS, 8))]
-                    for w in ws:
-                        gemm(path, xq, w, buffers[name], k, n)
-                    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    start.record(stream)
-                    for _ in range(2):
-                        for w in ws:
-                            gemm(path, xq, w, buffers[name], k, n)
-                    stop.record(stream)
-                    stop.synchronize()
-                    timings.append((start.elapsed_time(stop), path))
-                except RuntimeError:
-                    continue
-            best[name] = min(timings)[1]
-
-        def decode_step(gemm_only=False):
-            h = stack.h
-            n_res = rows * HIDDEN
-            for layer in stack.weights:
-                if not gemm_only:
-                    quantize(h, stack.q_hidden)
-                gemm(best["qkv"], stack.q_hidden, layer["qkv"], stack.qkv, HIDDEN, QKV)
-                if not gemm_only:
-                    quantize(stack.qkv[:, :HIDDEN], stack.q_hidden)
-                gemm(best["o"], stack.q_hidden, layer["o"], h, HIDDEN, HIDDEN)
-                lib.ttsref_residual_add_f32(h.data_ptr(), stack.residual.data_ptr(), n_res, sp)
-                if not gemm_only:
-                    quantize(h, stack.q_hidden)
-                gemm(best["gate_up"], stack.q_hidden, layer["gate_up"], stack.gu, HIDDEN, 2 * FFN)
-                if not gemm_only:
-                    rc = lib.ttsref_quantized_gated(stack.gu.data_ptr(), rows, FFN, BF16, stack.q_ffn.values.data_ptr(),
-                                                    stack.q_ffn.scales.data_ptr(), I8, 0, 0, 0, props.multi_processor_count,
-                                                    1, sp)
-                    assert rc == 0, lib.ttsref_last_error()
-                gemm(best["down"], stack.q_ffn, layer["down"], h, FFN, HIDDEN)
-                lib.ttsref_residual_add_f32(h.data_ptr(), stack.residual.data_ptr(), n_res, sp)
-
-        stack.h.copy_(stack.x)
-        decode_step()
-        stream.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            decode_step()
-        gemm_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(gemm_graph, stream=stream):
-            decode_step(gemm_only=True)
-    result = time_steps(args, torch, dist, world, device, stream, stack, graph, gemm_graph)
-    result["paths"] = {k: list(v) for k, v in best.items()}
-    return result
 
 
 def run_reference_cpu(args):
@@ -472,11 +578,65 @@ def run_reference_cpu(args):
     print(json.dumps(line))
 
 
+def run_case(spec):
+    """One small, self-ending case of a single quantized linear, meant to be run under a profiler:
+    `--case <qkv|o|gate_up|down> <rows> [mode] [launches]` runs quantize + GEMM `launches` times (default 6) over
+    enough distinct weight copies to exceed L2 (about 300 MB on the device in total), eagerly on one stream."""
+    import torch
+    from breeze_tts_cpp_b200 import ops
+    name, rows = spec[0], int(spec[1])
+    mode = spec[2] if len(spec) > 2 else "int8"
+    launches = int(spec[3]) if len(spec) > 3 else 6
+    k, n = SHAPES[name]
+    fmt = ops.format_of(mode)
+    group, _, rotation = ops.groups_of(mode)
+    device = torch.device("cuda", 0)
+    stream = torch.cuda.Stream(device=device)
+    with torch.cuda.stream(stream):
+        ctx = ops.Context(mode, device=0, stream=stream)
+        copies = max(2, min(launches, (300 << 20) // (n * k)))
+        weights = [ctx.quantize_rows(synth_weight(torch, n, k, SEED + c, device),
+                                     ops.RowScaledView.empty(n, k, fmt, group, rotation, device=device)) for c in range(copies)]
+        x = synth_activations(torch, rows, k, SEED, device, student_t=bool(group)).to(torch.bfloat16)
+        xq = ops.RowScaledView.empty(rows, k, fmt, group, rotation, device=device)
+        out = torch.empty(rows, n, dtype=torch.bfloat16, device=device)
+        path = ctx.prepare_quantized(rows, n, k)
+        ctx.quantize_rows(x, xq)
+        ctx.matmul(xq, weights[0], out)
+        stream.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for i in range(launches):
+            ctx.quantize_rows(x, xq)
+            ctx.matmul(xq, weights[i % copies], out)
+        stop.record(stream)
+        stop.synchronize()
+        status = ctx.status()
+        ctx.close()
+    print(f"{mode} {name} M={rows} K={k} N={n} path={path} avg {start.elapsed_time(stop) * 1e3 / launches:.2f} us per quantize+GEMM "
+          f"(eager launches), status {status}")
+    if status:
+        raise SystemExit(1)
+
+
 def workload_config(rows, world):
-    return {"workload": "c5_decoder_stack28_int8_decode (shapes of c2: QKV 2048->4096, O 2048->2048, gate+up 2048->12288, "
-                        "down 6144->2048; fp32 residual on O and down)",
+    return {"workload": "c5_decoder_stack28_int8_decode (per layer: residual+RMSNorm+quantize, QKV 2048->4096, row quantize, "
+                        "O 2048->2048, residual+RMSNorm+quantize, gate+up 2048->12288, SiLU-gate+quantize, down 6144->2048)",
             "layers": LAYERS, "streams_total": STREAMS, "rows_per_gpu": rows, "parallelism": f"dp{world} (replicated weights, no collective)",
-            "l2": "inputs larger than L2: 1.41 GB of distinct weights per step vs 126 MB L2", "timing": "CUDA events on the launch stream, CUDA-graph replay"}
+            "launches_per_step": LAUNCHES_PER_STEP,
+            "l2": "inputs larger than L2: 1.41 GB of distinct weights per step vs 126 MB L2",
+            "timing": "CUDA events on the launch stream, CUDA-graph replay; steps last about a millisecond, so the GPU stays at burst clocks"}
+
+
+def dram_traffic_per_launch(rows):
+    """Average DRAM bytes per GEMM launch of a step, from the per-shape ncu captures at M=64 scaled by the
+    algorithmic bytes of the row count in use; None until every shape has a capture."""
+    if any(v is None for v in NCU_DRAM_BYTES_M64.values()):
+        return None
+    total = 0.0
+    for name, (k, n) in SHAPES.items():
+        total += NCU_DRAM_BYTES_M64[name] * linear_bytes(rows, k, n, quantize=False) / linear_bytes(64, k, n, quantize=False)
+    return int(total / len(SHAPES))
 
 
 def main():
@@ -485,10 +645,14 @@ def main():
     parser.add_argument("--steps", type=int, default=50)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="b200q", choices=["b200q", "reference", "reference-cpu"])
-    parser.add_argument("--no-sweep", action="store_true", help="skip the per-shape extras (decode sweep, prefill, K-group)")
+    parser.add_argument("--no-configs", action="store_true", help="skip the per-configuration rows (c1-c4)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--case", nargs="+", metavar="ARG", help="profiling case: <qkv|o|gate_up|down> <rows> [mode] [launches]")
     args = parser.parse_args()
     args.warmup = max(3, args.warmup)
+    if args.case:
+        run_case(args.case)
+        return
 
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -509,27 +673,33 @@ def main():
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
-    from breeze_tts_cpp_b200.sharding import shard_streams
     if STREAMS % world:
         raise SystemExit("the 64 streams must divide over the GPUs")
-    rows = shard_streams(STREAMS, world, rank)[1]
+    rows = STREAMS // world
     peaks = measured_peaks()
 
     if args.impl == "reference":
-        result = run_reference(args, torch, dist, rank, world, device)
-        extras = {}
-        if result is None:
+        from tests import oracle_binding
+        lib = oracle_binding.load_reference()
+        if lib is None:
             if rank == 0:
                 print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libttsref.so (the reference's CUDA kernels) is not built"}))
             return
+        arm, stream, result = run_chain(args, torch, dist, rank, world, device,
+                                        lambda stream, r: ReferenceArm(torch, device, stream, r, lib))
     else:
-        result, extras = run_b200q(args, torch, dist, rank, world, device)
+        arm, stream, result = run_chain(args, torch, dist, rank, world, device,
+                                        lambda stream, r: B200QArm(torch, device, stream, r))
+
+    # whole-job numbers: work summed over ranks, time = the slowest rank
+    from breeze_tts_cpp_b200.sharding import whole_job_rate  # pure Python; loads no native code
+    seconds = {key: whole_job_rate(1.0, result[key] * 1e-3, dist, device)[2] for key in ("ms_value", "ms_e2e", "ms_gemm")}
 
     if rank == 0:
         total_bytes = step_bytes(rows) * world  # every GPU streams its own replica
-        ms_step = result["ms_value"] / args.steps
-        ms_e2e = result["ms_e2e"] / args.steps
-        ms_gemm = result["ms_gemm"] / args.steps
+        ms_step = seconds["ms_value"] * 1e3 / args.steps
+        ms_e2e = seconds["ms_e2e"] * 1e3 / args.steps
+        ms_gemm = seconds["ms_gemm"] * 1e3 / args.steps
         gemm_bytes = step_bytes(rows, gemm_only=True)
         achieved = gemm_bytes / (ms_gemm * 1e-3) / 1e9
         line = {
@@ -543,26 +713,29 @@ def main():
                     "h2d_bytes_per_step": result["h2d"], "d2h_bytes_per_step": result["d2h"]},
             "roofline": {"bound": "hbm", "kernel": "w8a8 GEMM launches of one step (112 launches, 4 shapes)",
                          "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": round(achieved / peaks["hbm_gbs"], 4), "frac_of_nominal_8TBps": round(achieved / 8000.0, 4),
+                         "frac": round(achieved / peaks["hbm_gbs"], 4), "frac_of_nominal_8TBps": round(achieved / NOMINAL_HBM_GBS, 4),
                          "peak_source": peaks["source"], "avg_launch_us": round(ms_gemm * 1e3 / (LAYERS * 4), 3),
                          "algorithmic_bytes_per_launch": gemm_bytes // (LAYERS * 4),
-                         # DRAM bytes per launch: the ncu capture of the gate+up launch at M=64 (profiles/) read
-                         # 25.40 MB for 26.92 MB algorithmic; the same ratio applied to the average launch.
-                         "traffic": int(gemm_bytes // (LAYERS * 4) * 25.40 / 26.92)},
+                         "traffic": dram_traffic_per_launch(rows),
+                         "traffic_source": "one-launch ncu captures of the four shapes at M=64, scaled by algorithmic bytes"},
             "clocks": result["clocks"],
         }
         if args.impl == "reference":
             line["impl"] = "reference"
-            line["reference_paths"] = result.get("paths")
+            line["reference_paths"] = {k: list(v) for k, v in arm.best.items()}
             line["cpu_baseline"] = {"value": line["value"], "unit": "GB/s", "cores": 0, "kind": "reference",
                                     "sample": "the reference's own CUDA kernels on this GPU (it has no CPU implementation of the path)"}
-            line["roofline"]["kernel"] = "reference GEMM launches of one step (+ its residual pass)"
+            line["roofline"]["kernel"] = "reference GEMM launches of one step"
+            line["roofline"]["traffic"] = None
         else:
             line["impl"] = "b200q"
-            line["gpu_launches"] = result["gpu_launches"]
+            line["gpu_launches"] = LAUNCHES_PER_STEP * args.steps
             if world == 1 and not args.no_cpu_baseline:
                 line["cpu_baseline"] = cpu_baseline(rows)
-            line.update(extras)
+            if world == 1 and not args.no_configs:
+                tensor_peaks = library_tensor_peaks(torch, device)
+                line["tensor_peaks"] = tensor_peaks
+                line["configs"] = config_rows(torch, device, stream, peaks, tensor_peaks)
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

@@ -46,6 +46,7 @@ SIGNATURES = {
     "b200q_quantized_norm": (C.c_int, (C.c_void_p, _PT, _PT, _PT, _PR, C.c_float, C.c_int32, _PT, *_ERR)),
     "b200q_quantized_gated": (C.c_int, (C.c_void_p, _PT, _PR, C.c_int32, *_ERR)),
     "b200q_prepare": (C.c_int, (C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _PP, *_ERR)),
+    "b200q_prepare_weight": (C.c_int, (C.c_void_p, _PR, *_ERR)),
     "b200q_seal": (C.c_int, (C.c_void_p, *_ERR)),
     "b200q_linear": (C.c_int, (C.c_void_p, _PR, _PR, _PT, _PE, *_ERR)),
     "b200q_quant_linear": (C.c_int, (C.c_void_p, _PP, _PR, _PR, _PT, _PE, *_ERR)),
@@ -57,9 +58,13 @@ SIGNATURES = {
     "b200q_linear_layer_forward": (C.c_int, (C.c_void_p, C.c_void_p, _PT, _PT, _PE, _PR, *_ERR)),
     "b200q_linear_layer_weight": (C.c_int, (C.c_void_p, _PR, *_ERR)),
     "b200q_quant_linear_static": (C.c_int, (C.c_int32, C.c_void_p, _PP, _PR, _PR, _PT, _PE, *_ERR)),
+    "b200q_static_status": (C.c_int, (C.c_int32, C.c_void_p, C.POINTER(C.c_int32), *_ERR)),
     "b200q_status": (C.c_int, (C.c_void_p, C.POINTER(C.c_int32), *_ERR)),
     "b200q_multiprocessors": (C.c_int, (C.c_void_p,)),
     "b200q_row_capacity": (C.c_int32, (C.c_int32, C.c_uint32)),
+    "b200q_candidates": (C.c_int, (C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _PP, C.c_int32, *_ERR)),
+    "b200q_path_cost": (C.c_double, (C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _PP, C.c_int32,
+                                     C.c_int32, *_ERR)),
     "b200q_plan_path": (C.c_int, (C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                   C.c_size_t, _PP, C.POINTER(C.c_size_t), *_ERR)),
 }

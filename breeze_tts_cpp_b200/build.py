@@ -28,6 +28,7 @@ SOURCES = [
     ("kernels/quant_linear.cu", []),
     ("kernels/quant_linear_static.cu", []),
     ("ops/quantized_gemm.cpp", []),
+    ("ops/quantization_policy.cpp", []),
     ("ops/context.cpp", []),
     ("ops/ops.cpp", []),
     ("layers/linear.cpp", []),

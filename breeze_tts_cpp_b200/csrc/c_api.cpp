@@ -5,6 +5,7 @@
 #include "ops/context.h"
 #include "ops/ops.h"
 #include "layers/linear.h"
+#include "ops/quantization_policy.h"
 #include <vector>
 #include <cstdio>
 #include <cstring>
@@ -124,6 +125,16 @@ int b200q_prepare(b200q_context *c, int32_t rows, int32_t channels, int32_t redu
         QuantizationGroups groups{activation_group, weight_group, 0};
         gpu.quantization->prepare(rows, channels, reduction, type_of(output_type), groups);
         put_path(chosen, gpu.quantization->planned_path(rows, channels, reduction, type_of(output_type), groups));
+    });
+}
+int b200q_prepare_weight(b200q_context *c, const b200q_row_scaled *weight, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        auto &gpu = context_of(c);
+        ExecutionScope scope(gpu);
+        auto w = scaled_of(weight);
+        w.validate();
+        if (w.values.device != gpu.device) throw std::invalid_argument("operand is not on the context's device");
+        gpu.quantization->prepare_weight(w.values);
     });
 }
 int b200q_seal(b200q_context *c, char *error, size_t capacity) {
@@ -261,5 +272,29 @@ int b200q_plan_path(int32_t rows, int32_t channels, int32_t reduction, int32_t a
         put_path(chosen, path);
         if (workspace_needed) *workspace_needed = quant_linear_workspace_bytes(path, problem);
     });
+}
+int b200q_candidates(int32_t rows, int32_t channels, int32_t reduction, int32_t activation_group, int32_t weight_group,
+                     int32_t format, b200q_path *paths, int32_t capacity, char *error, size_t error_capacity) {
+    int count = -1;
+    guarded(error, error_capacity, [&] {
+        auto found = quant_linear_candidates({rows, channels, reduction, activation_group, weight_group}, {}, type_of(format));
+        for (size_t i = 0; i < found.size() && int(i) < capacity; ++i) put_path(paths ? paths + i : nullptr, found[i]);
+        count = int(found.size());
+    });
+    return count;
+}
+double b200q_path_cost(int32_t rows, int32_t channels, int32_t reduction, int32_t activation_group, int32_t weight_group,
+                       int32_t format, const b200q_path *path, int32_t multiprocessors, int32_t gemm_only, char *error,
+                       size_t error_capacity) {
+    double cost = -1;
+    guarded(error, error_capacity, [&] {
+        if (!path) throw std::invalid_argument("null path");
+        KernelProblem problem{rows, channels, reduction, activation_group, weight_group};
+        LinearPath p{static_cast<LinearKind>(path->kind), path->tokens, path->channels, path->splits};
+        const ChipModel chip = ChipModel::b200(multiprocessors);
+        cost = gemm_only ? linear_cost(problem, p, type_of(format), chip)
+                         : linear_pipeline_cost(problem, p, type_of(format), chip, {}, true);
+    });
+    return cost;
 }
 }

@@ -3,6 +3,7 @@
 // switch without edits; `LinearKind::Tcgen05` is the only kind this build executes.
 #pragma once
 #include "core/quantization.h"
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 namespace tts {
@@ -16,12 +17,22 @@ void launch_quant_linear(LinearPath config, KernelProblem shape, const void *inp
                          const float *input_scales, const void *weights, const float *weight_scales,
                          void *output, void *workspace, size_t workspace_bytes, cudaStream_t stream,
                          Type format = Type::FP8, Type output_type = Type::BF16,
-                         const ops::Epilogue *finish = nullptr);
+                         const ops::Epilogue *finish = nullptr, const struct WeightMaps *prepared = nullptr);
 // Initialization only; the fused finish needs no extra resources on this path.
 KernelResources quant_linear_finish_resources(LinearPath, Type format, Type output_type);
 
 // --- additions of this build -------------------------------------------------------------------
-// Tile/split choice for a problem: tokens = token tile (16..256), channels = 128, splits = split-K.
+// The TMA descriptor of a weight matrix, built once while plans are prepared and handed to
+// `launch_quant_linear` through its last, optional argument; a launch whose weights it does not
+// describe (or that passes none) builds the descriptor itself.
+struct WeightMaps {
+    CUtensorMap values;
+    const void *weights = nullptr;
+    int channels = 0, reduction = 0;
+};
+WeightMaps quant_linear_weight_maps(const void *weights, int channels, int reduction);
+// Tile/split choice for a problem with the B200 chip model: tokens = token tile (16..256),
+// channels = 128, splits = split-K. Shorthand for `select_linear` (ops/quantization_policy.h).
 LinearPath select_tcgen05_path(KernelProblem, Type format, int multiprocessors, size_t workspace_bytes);
 // Bytes of caller workspace a path needs (header + split-K partials).
 size_t quant_linear_workspace_bytes(LinearPath, KernelProblem);

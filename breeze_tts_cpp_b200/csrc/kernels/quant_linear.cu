@@ -7,20 +7,17 @@
 #include "kernels/quant_prefill_pair_sm100.cuh"
 #include "kernels/quant_prefill_grouped_sm100.cuh"
 #include "ops/epilogue.h"
-#include <cuda.h>
-#include <cstdlib>
+#include "ops/quantization_policy.h"
+#include <atomic>
 #include <cudaTypedefs.h>
 #include <map>
 #include <mutex>
 #include <stdexcept>
 #include <string>
-#include <tuple>
 
 namespace tts {
 namespace {
 using namespace b200;
-constexpr size_t kSmemCompact = 108 * 1024; // two CTAs per SM
-constexpr size_t kSmemBudget = 208 * 1024; // dynamic part per CTA; leaves room on the SM for a co-resident producer CTA of the next kernel
 
 void check(cudaError_t status, const char *what) {
     if (status != cudaSuccess)
@@ -40,16 +37,11 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_tiled() {
     return fn;
 }
 
+// Tensor maps are returned by value (128 bytes, encoded on the host without a driver round trip):
+// the launch copies them into the kernel's parameters, so nothing has to outlive the call.
 // Row-major one-byte matrix [rows, k]; box = 128 bytes of K by `box_rows` rows, 128B swizzle,
 // out-of-range rows/columns read as zero (so ragged M, N and K tails need no special code).
-const CUtensorMap &tensor_map(const void *base, int rows, int k, int box_rows, bool weights) {
-    using Key = std::tuple<const void *, int, int, int>;
-    static std::map<Key, CUtensorMap> cache;
-    static std::mutex guard;
-    std::lock_guard<std::mutex> lock(guard);
-    Key key{base, rows, k, box_rows};
-    auto it = cache.find(key);
-    if (it != cache.end()) return it->second;
+CUtensorMap operand_map(const void *base, int rows, int k, int box_rows, bool weights) {
     if (reinterpret_cast<uintptr_t>(base) % 16 || k % 16)
         throw std::invalid_argument("quantized operand must be 16-byte aligned with K a multiple of 16");
     CUtensorMap map;
@@ -64,20 +56,12 @@ const CUtensorMap &tensor_map(const void *base, int rows, int k, int box_rows, b
                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (status != CUDA_SUCCESS)
         throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(status)));
-    if (cache.size() > 4096) cache.clear();
-    return cache.emplace(key, map).first->second;
+    return map;
 }
 
 // Group-major fp32 scales [K/128, rows]: box = 128 consecutive rows of one K group, no swizzle,
 // rows past the end read as zero.
-const CUtensorMap &scale_map(const float *base, int rows, int groups) {
-    using Key = std::tuple<const void *, int, int>;
-    static std::map<Key, CUtensorMap> cache;
-    static std::mutex guard;
-    std::lock_guard<std::mutex> lock(guard);
-    Key key{base, rows, groups};
-    auto it = cache.find(key);
-    if (it != cache.end()) return it->second;
+CUtensorMap scale_map(const float *base, int rows, int groups) {
     if (reinterpret_cast<uintptr_t>(base) % 16 || rows % 4)
         throw std::invalid_argument("K-group scales must be 16-byte aligned with a row count that is a multiple of 4");
     CUtensorMap map;
@@ -90,39 +74,7 @@ const CUtensorMap &scale_map(const float *base, int rows, int groups) {
                                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (status != CUDA_SUCCESS)
         throw std::runtime_error("cuTensorMapEncodeTiled (scales) failed with code " + std::to_string(int(status)));
-    if (cache.size() > 4096) cache.clear();
-    return cache.emplace(key, map).first->second;
-}
-
-template <Type F, bool Grouped, int BN> auto kernel_of() { return w8a8_tcgen05_gemm<F, Grouped, BN>; }
-
-struct Shape {
-    int stages, owned_passes;
-    size_t tile_region, smem;
-};
-// Shared memory of one CTA: alignment slack + pipeline stages (unsplit: later the transposed
-// [token][channel] tile of 4-byte partials) + split-K slots the cluster peers push into +
-// K-group scales of the CTA's K range.
-Shape shape_for(int bn, bool grouped, int kb_per_split, int splits) {
-    const size_t stage = size_t(kBlockChannels + bn) * kBlockK;
-    const size_t transposed = splits == 1 ? size_t(bn) * kBlockChannels * sizeof(float) : 0;
-    const int passes = (bn + kRowsPerPass - 1) / kRowsPerPass;
-    const int owned = splits > 1 ? (passes + splits - 1) / splits : 0;
-    const size_t reduce = size_t(splits > 1 ? splits : 0) * owned * kRowsPerPass * kBlockChannels * sizeof(float);
-    const size_t scales = grouped ? size_t(kb_per_split) * (bn + kBlockChannels) * sizeof(float) : 0;
-    const size_t fixed = 1024 + reduce + scales;
-    if (fixed + std::max(2 * stage, transposed) > kSmemBudget)
-        throw std::invalid_argument("quantized GEMM: this tile/split combination exceeds shared memory; use more splits");
-    // As many stages as fit (capped by the K blocks of one CTA): the ring is what gets prefetched
-    // while the upstream kernel is still running. Measured on the decode chain, deep rings with one
-    // CTA per SM beat half-size rings with two co-resident CTAs.
-    int stages = int((kSmemBudget - fixed) / stage);
-    stages = std::max(2, std::min({stages, kMaxStages, std::max(2, kb_per_split)}));
-#ifdef B200Q_TIMING
-    if (const char *forced = std::getenv("B200Q_STAGES")) stages = std::max(2, std::min(stages, std::atoi(forced)));
-#endif
-    const size_t region = std::max(size_t(stages) * stage, transposed);
-    return {stages, owned, region, fixed + region};
+    return map;
 }
 
 // Split-K launches group the `splits` CTAs of one output tile into a thread-block cluster (1,1,splits).
@@ -174,13 +126,16 @@ template <Type F, bool Grouped, int BN> void raise_limit() {
 }
 constexpr size_t kPrefillSmem = 1024 + size_t(kPrefillStages) * (kBlockChannels + kPrefillTokens) * kBlockK + kPrefillPatchBytes;
 int multiprocessor_count() {
-    static int cached[64] = {};
+    static std::atomic<int> cached[64];
     int device = 0;
     check(cudaGetDevice(&device), "cudaGetDevice");
     if (device < 0 || device >= 64) return 148;
-    if (!cached[device])
-        check(cudaDeviceGetAttribute(&cached[device], cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute");
-    return cached[device];
+    int count = cached[device].load(std::memory_order_relaxed);
+    if (!count) {
+        check(cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute");
+        cached[device].store(count, std::memory_order_relaxed);
+    }
+    return count;
 }
 template <Type F>
 void launch_prefill(const CUtensorMap &map_w, const CUtensorMap &map_x, const PrefillArgs &args, cudaStream_t stream) {
@@ -286,59 +241,22 @@ int quant_linear_status(const void *workspace, cudaStream_t stream) {
 size_t quant_linear_workspace_bytes(LinearPath, KernelProblem) { return kWorkspaceHeader; }
 
 LinearPath select_tcgen05_path(KernelProblem p, Type format, int sms, size_t workspace_bytes) {
-    (void)format;
-    (void)workspace_bytes; // the GEMM keeps its split-K partials in shared memory
-    if (sms <= 0) sms = 148;
-    const bool grouped = p.input_group || p.weight_group;
-    const int max_tokens = grouped ? 128 : 256;
-    int bn = 16;
-    while (bn < max_tokens && bn < p.rows) bn *= 2;
-    const int n_tiles = (p.channels + kBlockChannels - 1) / kBlockChannels;
-    const int m_tiles = (p.rows + bn - 1) / bn;
-    const int64_t tiles = int64_t(n_tiles) * m_tiles;
-    const int kb_total = (p.reduction + kBlockK - 1) / kBlockK;
-    LinearPath best{LinearKind::Tcgen05, bn, kBlockChannels, 1};
-    // Cost in "K blocks streamed by the busiest SM" plus a fixed per-CTA prologue/epilogue, with the
-    // split reduction growing with the tile it moves through shared memory. Memory-bound shapes want
-    // every SM to stream a disjoint weight slab; clusters of `splits` CTAs must fit the machine.
-    // Estimated microseconds: a fixed launch/prologue/epilogue latency plus the streaming time of the
-    // busiest SM, which is bounded by what one SM can pull (about 85 GB/s) and by its share of HBM.
-    double best_cost = 1e300;
-    const double stage_bytes = double(kBlockChannels + bn) * kBlockK;
-    for (int splits = 1; splits <= std::min(kb_total, 4); ++splits) {
-        const int per_split = (kb_total + splits - 1) / splits;
-        Shape shape{};
-        try {
-            shape = shape_for(bn, grouped, per_split, splits);
-        } catch (const std::invalid_argument &) {
-            continue;
-        }
-        const int per_sm = shape.smem <= kSmemCompact ? 2 : 1;
-        const int64_t ctas = tiles * splits;
-        const int64_t slots = int64_t(sms) * per_sm / splits * splits; // whole clusters only
-        const double waves = double((ctas + slots - 1) / slots);
-        const double per_sm_stream = per_split * stage_bytes / 85e3;
-        const double hbm_stream = double(std::min<int64_t>(ctas, slots)) * per_split * stage_bytes / 5.5e6;
-        const double cost = 4.0 + waves * std::max(per_sm_stream, hbm_stream) + (splits > 1 ? 0.3 + 0.2 * splits : 0.0);
-        if (cost < best_cost - 1e-9) {
-            best_cost = cost;
-            best = LinearPath{LinearKind::Tcgen05, bn, kBlockChannels, splits};
-        }
-    }
-#ifdef B200Q_TIMING
-    // experiment knob: "K:N=S,..." e.g. "2048:4096=4,6144:2048=3"
-    if (const char *forced = std::getenv("B200Q_SPLITS")) {
-        std::string text(forced), key = std::to_string(p.reduction) + ":" + std::to_string(p.channels) + "=";
-        auto at = text.find(key);
-        if (at != std::string::npos) best.splits = std::atoi(text.c_str() + at + key.size());
-    }
-#endif
-    return best;
+    return select_linear(p, KernelLimits{false, 0, workspace_bytes}, format, ChipModel::b200(sms));
+}
+
+WeightMaps quant_linear_weight_maps(const void *weights, int channels, int reduction) {
+    WeightMaps maps;
+    maps.values = operand_map(weights, channels, reduction, kBlockChannels, true);
+    maps.weights = weights;
+    maps.channels = channels;
+    maps.reduction = reduction;
+    return maps;
 }
 
 void launch_quant_linear(LinearPath config, KernelProblem shape, const void *input, const float *xs,
                          const void *weights, const float *ws, void *y, void *workspace, size_t bytes,
-                         cudaStream_t stream, Type format, Type output_type, const ops::Epilogue *finish) {
+                         cudaStream_t stream, Type format, Type output_type, const ops::Epilogue *finish,
+                         const WeightMaps *prepared) {
     const bool grouped = shape.input_group || shape.weight_group;
     if (output_type != Type::BF16 && output_type != Type::F16 &&
         !(output_type == Type::I32 && format == Type::I8 && !grouped && !finish))
@@ -391,41 +309,44 @@ void launch_quant_linear(LinearPath config, KernelProblem shape, const void *inp
         vector_io = vector_io && aligned16(e.residual_f32.data);
     }
     args.vector_io = vector_io;
-    const CUtensorMap &map_w = tensor_map(weights, shape.channels, shape.reduction, kBlockChannels, true);
+    // The weight map is the caller's prepared one when it describes these weights, else built here.
+    CUtensorMap local_w;
+    const bool reuse = prepared && prepared->weights == weights && prepared->channels == shape.channels &&
+                       prepared->reduction == shape.reduction;
+    if (!reuse) local_w = operand_map(weights, shape.channels, shape.reduction, kBlockChannels, true);
+    const CUtensorMap &map_w = reuse ? prepared->values : local_w;
     // Compute-bound shapes with a plain epilogue take the persistent, double-buffered kernels:
     // CTA pairs (each CTA loads half of the token tile) when there are at least two channel tiles.
     if (!grouped && bn == kPrefillTokens && splits == 1 && !args.ep.chain && output_type != Type::I32 && args.vector_io) {
         PrefillArgs prefill{args.m, args.n, args.k, xs, ws, y, int(output_type), args.ep.residual_f32, args.status};
-        bool pair = shape.channels >= 2 * kBlockChannels;
-#ifdef B200Q_TIMING
-        if (std::getenv("B200Q_NOPAIR")) pair = false;
-#endif
-        if (pair) {
-            const CUtensorMap &map_half = tensor_map(input, shape.rows, shape.reduction, kPrefillTokens / 2, false);
+        if (shape.channels >= 2 * kBlockChannels) {
+            const CUtensorMap map_half = operand_map(input, shape.rows, shape.reduction, kPrefillTokens / 2, false);
             if (format == Type::I8) launch_prefill_pair<Type::I8>(map_w, map_half, prefill, stream);
             else launch_prefill_pair<Type::FP8>(map_w, map_half, prefill, stream);
             return;
         }
-        const CUtensorMap &map_x = tensor_map(input, shape.rows, shape.reduction, bn, false);
+        const CUtensorMap map_x = operand_map(input, shape.rows, shape.reduction, bn, false);
         if (format == Type::I8) launch_prefill<Type::I8>(map_w, map_x, prefill, stream);
         else launch_prefill<Type::FP8>(map_w, map_x, prefill, stream);
         return;
     }
     // Compute-bound K-group shapes (both operands grouped by 128, enough 128x128 tiles to fill most of
-    // the GPU, plain epilogue) take the persistent K-group kernel; it never splits K.
-    if (grouped && shape.input_group == kBlockK && shape.weight_group == kBlockK && bn == kGroupedTokens &&
+    // the GPU, plain epilogue, no split) take the persistent K-group kernel.
+    if (grouped && shape.input_group == kBlockK && shape.weight_group == kBlockK && bn == kGroupedTokens && splits == 1 &&
         !args.ep.chain && args.vector_io && shape.rows % 4 == 0 &&
         int64_t(n_tiles) * ((shape.rows + kGroupedTokens - 1) / kGroupedTokens) >= int64_t(multiprocessor_count()) * 2 / 3) {
         PrefillArgs prefill{args.m, args.n, args.k, xs, ws, y, int(output_type), args.ep.residual_f32, args.status};
-        const CUtensorMap &map_x = tensor_map(input, shape.rows, shape.reduction, kGroupedTokens, false);
-        const CUtensorMap &map_sw = scale_map(ws, shape.channels, kb_total);
-        const CUtensorMap &map_sx = scale_map(xs, shape.rows, kb_total);
+        const CUtensorMap map_x = operand_map(input, shape.rows, shape.reduction, kGroupedTokens, false);
+        const CUtensorMap map_sw = scale_map(ws, shape.channels, kb_total);
+        const CUtensorMap map_sx = scale_map(xs, shape.rows, kb_total);
         if (format == Type::I8) launch_prefill_grouped<Type::I8>(map_w, map_x, map_sw, map_sx, prefill, stream);
         else launch_prefill_grouped<Type::FP8>(map_w, map_x, map_sw, map_sx, prefill, stream);
         return;
     }
-    const CUtensorMap &map_x = tensor_map(input, shape.rows, shape.reduction, bn, false);
-    Shape launch = shape_for(bn, grouped, (kb_total + splits - 1) / splits, splits);
+    const CUtensorMap map_x = operand_map(input, shape.rows, shape.reduction, bn, false);
+    LaunchShape launch = launch_shape(bn, grouped, (kb_total + splits - 1) / splits, splits);
+    if (!launch.fits)
+        throw std::invalid_argument("quantized GEMM: this tile/split combination exceeds shared memory; use more splits");
     // A K-group CTA allocates all 512 columns of tensor memory, so two of them must never share a
     // multiprocessor (the second allocation would wait for the first CTA, and with split-K clusters
     // two such waits can form a cycle): ask for more than half of the shared memory.

@@ -28,20 +28,15 @@
 //                    (fp32 residual, bias, bf16 store) is a coalesced 16-byte vector.
 #pragma once
 #include "kernels/sm100_ptx.cuh"
+#include "kernels/quant_linear_geometry.h"
 #include "core/tensor.h"
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 namespace tts::b200 {
 
-constexpr int kBlockChannels = 128; // MMA M: weight rows per tile
-constexpr int kBlockK = 128;        // bytes of K per pipeline stage (one 128B-swizzled TMA box)
-constexpr int kMaxStages = 12;
 constexpr int kGemmThreads = 320;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2-9 epilogue
 constexpr int kEpilogueThreads = 256;
-constexpr int kRowsPerPass = 16;    // token rows the epilogue warps finish per pass (16 threads x 8 channels per row)
-
-constexpr int kMaxSplits = 8;       // portable thread-block cluster size
 
 // Workspace carve-up (owner zeroes the first kWorkspaceHeader bytes once). The GEMM itself needs
 // no scratch; only the status word lives here.
@@ -57,22 +52,6 @@ struct FusedEpilogue {
     int residual_ld = 0;
     int chain = 0;                      // nonzero when anything beyond residual_f32 is requested
 };
-
-#ifdef B200Q_TIMING
-// Debug build only: CTA 0 keeps (event -> global nanosecond timer) in shared memory and appends the
-// records to a log 64 KiB into the workspace when it exits; word 0 of the log is the record count.
-#define B200Q_STAMP(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { \
-    unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) :: "memory"); stamp_log[slot] = t_; } } while (0)
-#define B200Q_CLOCK(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) stamp_log[slot] = (unsigned long long)clock64(); } while (0)
-#define B200Q_STAMP_FLUSH() do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { \
-    unsigned long long *log_ = reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(a.status) - kStatusOffset + 65536); \
-    unsigned long long at_ = atomicAdd(log_, 28ull); \
-    if (at_ < 60000) for (int s_ = 0; s_ < 28; ++s_) { log_[1 + 2 * (at_ + s_)] = (unsigned long long)(a.n) << 32 | (unsigned long long)(s_); log_[2 + 2 * (at_ + s_)] = stamp_log[s_]; } } } while (0)
-#else
-#define B200Q_STAMP(slot) do { } while (0)
-#define B200Q_CLOCK(slot) do { } while (0)
-#define B200Q_STAMP_FLUSH() do { } while (0)
-#endif
 
 struct GemmArgs {
     int m, n, k;
@@ -155,11 +134,6 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ float sx_tile[BN]; // per-row activation scales of this token tile
-#ifdef B200Q_TIMING
-    __shared__ unsigned long long stamp_log[28];
-    if (threadIdx.x < 28) stamp_log[threadIdx.x] = 0;
-    __syncthreads();
-#endif
 
     // Dynamic shared memory, 1024-byte aligned for the swizzled TMA boxes:
     //   [pipeline stages | split-K slots pushed by the cluster peers | K-group scales]
@@ -184,7 +158,6 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const int tile_linear = blockIdx.y * gridDim.x + blockIdx.x;
     const int valid_tokens = min(BN, a.m - m0);
 
-    if (threadIdx.x == 0) B200Q_STAMP(0);
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
@@ -209,7 +182,6 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     // The next kernel in the stream may begin its own prologue; peers learn that this CTA is running.
     ptx::launch_dependents();
     if (splits > 1) ptx::cluster_arrive();
-    if (threadIdx.x == 0) B200Q_STAMP(1);
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -227,7 +199,6 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 ptx::tma_load_2d(tiles_base + uint32_t(i) * kStageBytes, &map_w, bar, (kb_begin + i) * kBlockK, n0);
             }
             ptx::wait_for_upstream();
-            B200Q_STAMP(9);
             ptx::mbar_arrive_expect_tx(ptx::smem_u32(&x_full), uint32_t(ahead) * kTokenBytes);
             for (int i = 0; i < ahead; ++i)
                 ptx::tma_load_2d(tiles_base + uint32_t(i) * kStageBytes + kWeightBytes, &map_x,
@@ -257,7 +228,6 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             for (int i = 0; i < ahead && ok; ++i) ok = ptx::mbar_wait(ptx::smem_u32(&full_bar[i]), 0u, abort_ptr);
             ok = ok && ptx::mbar_wait(ptx::smem_u32(&x_full), 0u, abort_ptr);
             ok = __all_sync(0xffffffffu, ok);
-            if (lane == 0) { B200Q_STAMP(2); B200Q_CLOCK(10); }
             // The prefetched stages need no barrier at all any more, so their MMAs go out back to back
             // (any shared-memory access between MMA issues stalls the issuing warp for a couple of
             // hundred cycles). Stage i holds K block i here; in K-group mode K block i also has
@@ -281,7 +251,6 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 }
                 first = burst;
             }
-            if (lane == 0) B200Q_CLOCK(12);
             int stage = first == a.stages ? 0 : first;
             uint32_t phase = first == a.stages ? 1u : 0u;
             // Refilled stages arrive at the rate memory delivers them, one barrier each.
@@ -306,12 +275,10 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 __syncwarp();
                 if (++stage == a.stages) { stage = 0; phase ^= 1u; }
             }
-            if (lane == 0) B200Q_CLOCK(11);
             if (ptx::elect_one()) {
                 if (!Grouped) ptx::tcgen05_commit(ptx::smem_u32(&acc_full[0]));
             }
             __syncwarp();
-            if (lane == 0) B200Q_STAMP(3);
         }
         if (splits > 1) ptx::cluster_wait();
     } else {
@@ -379,7 +346,6 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         if constexpr (!Grouped) {
             for (int c = e_thread; c < BN; c += kEpilogueThreads) sx_tile[c] = c < valid_tokens ? a.sx[m0 + c] : 0.f;
             ok = ptx::mbar_wait(ptx::smem_u32(&acc_full[0]), 0, abort_ptr);
-            if (e_thread == 0) B200Q_STAMP(4);
             ptx::tcgen05_fence_after();
             if (splits > 1) ptx::cluster_wait(); // every peer is running: its shared memory may be written
             if (ok) {
@@ -441,7 +407,6 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     }
                 }
             }
-            if (e_thread == 0) B200Q_STAMP(4);
             if (splits > 1) ptx::cluster_wait();
             if (ok) {
                 // Outer scales exist only when just one operand carries K-group scales.
@@ -463,13 +428,11 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 }
             }
         }
-        if (e_thread == 0) B200Q_STAMP(7);
         ptx::tcgen05_fence_before();
 
         // ---- phase boundary: rows are where their finisher will read them.
         if (splits > 1) ptx::cluster_sync();
         else asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (e_thread == 0) B200Q_STAMP(8);
 
         // ---- phase 2: finish token rows; every global access is a 16-byte vector on a 256-byte row.
         // The common case (bf16 out, aligned rows, nothing but an optional fp32 residual) takes a lean
@@ -615,20 +578,10 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 }
             }
         }
-        if (e_thread == 0) B200Q_STAMP(5);
     }
     if (warp < 2 && splits > 1) ptx::cluster_sync(); // the producer/MMA warps' share of the phase barrier
 
     __syncthreads(); // tensor memory is drained and nobody else will touch this CTA's shared memory
-    if (threadIdx.x == 0) { B200Q_STAMP(6); B200Q_STAMP_FLUSH(); }
-#ifdef B200Q_TIMING
-    if (threadIdx.x == 0) { // every CTA: its own end time (event 20)
-        unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) :: "memory");
-        unsigned long long *log_ = reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(a.status) - kStatusOffset + 65536);
-        unsigned long long at_ = atomicAdd(log_, 1ull);
-        if (at_ < 60000) { log_[1 + 2 * at_] = (unsigned long long)(a.n) << 32 | 20ull; log_[2 + 2 * at_] = t_; }
-    }
-#endif
     if (warp == 1) {
         ptx::tcgen05_fence_after();
         ptx::tmem_dealloc(tmem_base, kTmemColumns);

@@ -27,7 +27,6 @@
 
 namespace tts::b200 {
 
-constexpr int kGroupedTokens = 128;
 constexpr int kGroupedStages = 5;
 constexpr int kGroupedAccumulators = 4;
 constexpr int kScaleSlots = 8;
@@ -241,7 +240,11 @@ w8a8_tcgen05_prefill_grouped(const __grid_constant__ CUtensorMap map_w, const __
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&scale_empty[slot]));
             }
-            if (!ok || *abort_ptr) break;
+            // All eight warps decide together whether the tile is stored (a warp that left alone would
+            // strand the three that share its staging patch); the same barrier keeps two consecutive
+            // tiles from meeting in one patch.
+            ok = ptx::barrier_and(1, kEpilogueThreads, ok && !*abort_ptr);
+            if (!ok) break;
             // ---- tile finished: 16-token chunks out through the staging patches.
 #pragma unroll
             for (int k = 0; k < 4; ++k) {

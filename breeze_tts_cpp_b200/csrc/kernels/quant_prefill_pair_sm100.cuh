@@ -23,16 +23,6 @@
 
 namespace tts::b200 {
 
-#ifdef B200Q_TIMING
-// Debug build: cluster 0 / leader records per-tile times (global ns timer) 256 KiB into the workspace:
-// slot = local_tile * 8 + event.
-#define B200Q_PAIR_STAMP(local, event) do { if (blockIdx.x == 0 && (local) < 64) { unsigned long long t_; \
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) :: "memory"); \
-    reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(a.status) - kStatusOffset + 262144)[(local) * 8 + (event)] = t_; } } while (0)
-#else
-#define B200Q_PAIR_STAMP(local, event) do { } while (0)
-#endif
-
 constexpr int kPairStages = 6;
 
 template <Type F>
@@ -118,17 +108,14 @@ w8a8_tcgen05_prefill_pair(const __grid_constant__ CUtensorMap map_w, const __gri
             bool ok = true;
             for (int tile = cluster_id; tile < tiles && ok; tile += clusters, ++local) {
                 const int buffer = local & 1;
-                if (lane == 0) B200Q_PAIR_STAMP(local, 0);
                 ok = ptx::mbar_wait(ptx::smem_u32(&acc_empty[buffer]), ((uint32_t(local) >> 1) & 1u) ^ 1u, abort_ptr);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                if (lane == 0) B200Q_PAIR_STAMP(local, 1);
                 ptx::tcgen05_fence_after();
                 const uint32_t d = tmem_base + uint32_t(buffer * BN);
                 for (int kb = 0; kb < kb_count; ++kb) {
                     ok = __all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_ptr));
                     if (!ok) break;
-                    if (kb == 0 && lane == 0) B200Q_PAIR_STAMP(local, 2);
                     ptx::tcgen05_fence_after();
                     const uint32_t tile_smem = tiles_base + uint32_t(stage) * kStageBytes;
                     const uint32_t lo_w = ptx::smem_desc_lo_k128(tile_smem), lo_x = ptx::smem_desc_lo_k128(tile_smem + kWeightBytes);
@@ -142,7 +129,6 @@ w8a8_tcgen05_prefill_pair(const __grid_constant__ CUtensorMap map_w, const __gri
                 }
                 if (ok && ptx::elect_one()) ptx::tcgen05_commit_pair(ptx::smem_u32(&acc_full[buffer]), 3);
                 __syncwarp();
-                if (lane == 0) B200Q_PAIR_STAMP(local, 3);
             }
         }
     } else {
@@ -162,10 +148,10 @@ w8a8_tcgen05_prefill_pair(const __grid_constant__ CUtensorMap map_w, const __gri
             const int n = n0 + quadrant * 32 + lane;
             const float scale_w = n < a.n ? a.sw[n] : 0.f;
             sx_tile[buffer][e_thread] = e_thread < valid_tokens ? a.sx[m0 + e_thread] : 0.f;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            if (e_thread == 0) B200Q_PAIR_STAMP(local, 4);
-            if (!ptx::mbar_wait(ptx::smem_u32(&acc_full[buffer]), (uint32_t(local) >> 1) & 1u, abort_ptr)) break;
-            if (e_thread == 0) B200Q_PAIR_STAMP(local, 5);
+            // One barrier publishes the scales and makes the verdict of the wait common to all eight
+            // warps: they leave the loop together or not at all.
+            if (!ptx::barrier_and(1, kEpilogueThreads, ptx::mbar_wait(ptx::smem_u32(&acc_full[buffer]), (uint32_t(local) >> 1) & 1u, abort_ptr)))
+                break;
             ptx::tcgen05_fence_after();
 #pragma unroll 1
             for (int chunk = half; chunk < BN / 16; chunk += 2) {
@@ -181,7 +167,6 @@ w8a8_tcgen05_prefill_pair(const __grid_constant__ CUtensorMap map_w, const __gri
             ptx::tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_rank(ptx::smem_u32(&acc_empty[buffer]), 0));
-            if (e_thread == 0) B200Q_PAIR_STAMP(local, 6);
         }
         ptx::tcgen05_fence_before();
     }

@@ -18,7 +18,6 @@
 
 namespace tts::b200 {
 
-constexpr int kPrefillTokens = 256;
 constexpr int kPrefillStages = 4;
 constexpr int kPrefillPatchBytes = 2 * 2 * 16 * kBlockChannels * 2; // two chunk groups x two parities x [16][128] 16-bit
 
@@ -202,8 +201,10 @@ w8a8_tcgen05_prefill(const __grid_constant__ CUtensorMap map_w, const __grid_con
             const float scale_w = n < a.n ? a.sw[n] : 0.f;
             // Stage this tile's activation scales while the tensor cores are still busy with it.
             sx_tile[buffer][e_thread] = e_thread < valid_tokens ? a.sx[m0 + e_thread] : 0.f;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            if (!ptx::mbar_wait(ptx::smem_u32(&acc_full[buffer]), (uint32_t(local) >> 1) & 1u, abort_ptr)) break;
+            // One barrier publishes the scales and makes the verdict of the wait common to all eight
+            // warps: they leave the loop together or not at all.
+            if (!ptx::barrier_and(1, kEpilogueThreads, ptx::mbar_wait(ptx::smem_u32(&acc_full[buffer]), (uint32_t(local) >> 1) & 1u, abort_ptr)))
+                break;
             ptx::tcgen05_fence_after();
 #pragma unroll 1
             for (int chunk = half; chunk < BN / 16; chunk += 2) {

@@ -306,6 +306,18 @@ __device__ __forceinline__ bool pair_barrier_and(bool ok) {
                  : "memory");
     return all != 0;
 }
+// The same over any named barrier: every one of the `threads` participants learns whether all of
+// them passed `ok`. Used where several warps must agree to leave a loop together, because a warp
+// that left alone would strand its siblings at their next named barrier.
+__device__ __forceinline__ bool barrier_and(uint32_t id, uint32_t threads, bool ok) {
+    uint32_t all;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %3, 0;\n\tbar.red.and.pred p, %1, %2, q;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(all)
+                 : "r"(id), "r"(threads), "r"(uint32_t(ok))
+                 : "memory");
+    return all != 0;
+}
 // One lane of a converged warp; the same lane every time for the same mask.
 __device__ __forceinline__ bool elect_one() {
     uint32_t elected;

@@ -52,8 +52,11 @@ Linear Linear::quantize(const std::vector<TensorView> &parts, Quantization mode,
             offset += p.size();
         }
         ops::quantize_rows(gathered.view(rows, columns, source_type), whole);
-        if (cudaStreamSynchronize(gpu.stream) != cudaSuccess) throw std::runtime_error("weight quantization failed");
     }
+    // The GEMM prefetches weight tiles and weight scales ahead of its wait on the preceding kernel,
+    // so a weight must be complete on the device before the first GEMM that uses it is enqueued.
+    if (cudaStreamSynchronize(execution_context(device).stream) != cudaSuccess)
+        throw std::runtime_error("weight quantization failed");
     Linear layer(whole, source_type, bias);
     layer.values_ = values;
     layer.scales_ = scales;

@@ -6,6 +6,7 @@
 #include "core/buffer.h"
 #include "core/quantization.h"
 #include <algorithm>
+#include <cstdint>
 
 namespace tts {
 class QuantizationWorkspace {
@@ -26,6 +27,9 @@ class QuantizationWorkspace {
         if (rows < 1 || capacity.columns < 0 || capacity.scales_per_row < 0 ||
             bool(capacity.columns) != bool(capacity.scales_per_row))
             throw std::invalid_argument("invalid quantization workspace capacity");
+        if (capacity.columns && (size_t(rows) > SIZE_MAX / size_t(capacity.columns) ||
+                                 size_t(rows) > SIZE_MAX / sizeof(float) / size_t(capacity.scales_per_row)))
+            throw std::overflow_error("quantization workspace size overflow");
         values_ = Buffer(size_t(rows) * capacity.columns);
         scales_ = Buffer(size_t(rows) * capacity.scales_per_row * sizeof(float));
     }

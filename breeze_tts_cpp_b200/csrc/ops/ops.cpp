@@ -27,6 +27,7 @@ void prepare_quantized(TensorView weight, int rows, int output_channels, int inp
     auto &gpu = execution_context(weight);
     if (!gpu.quantization) throw std::logic_error("context was created without a quantization mode");
     gpu.quantization->prepare(rows, output_channels, input_channels, type, groups);
+    if (weight.rows == output_channels && weight.cols == input_channels) gpu.quantization->prepare_weight(weight);
     gpu.quantization->prepare_finish(rows, output_channels, input_channels, type, epilogue, groups);
 }
 // reference: src/ops/basic.cpp:54-58

@@ -1,6 +1,7 @@
 #include "ops/quantized_gemm.h"
 #include "kernels/quant_dispatch.h"
 #include "ops/epilogue.h"
+#include "ops/quantization_policy.h"
 #include <map>
 #include <tuple>
 
@@ -35,6 +36,10 @@ struct QuantizedGemm::Impl {
     int multiprocessors = 0;
     bool sealed = false;
     std::map<PlanKey, Plan> plans;
+    // TMA descriptors of the weight matrices announced before seal(), looked up by pointer at run time
+    // (a few tree steps; weights that were never announced get their descriptor built per launch).
+    std::map<const void *, WeightMaps> weight_maps;
+    ChipModel chip;
     SelectionStats stats;
 
     const Plan *find(int rows, int channels, int reduction, Type type, int input_group, int weight_group) const {
@@ -43,11 +48,12 @@ struct QuantizedGemm::Impl {
     }
     void run(const Plan &plan, const RowScaledView &input, const RowScaledView &weight, const TensorView &output,
              const ops::Epilogue *finish) {
+        const auto known = weight_maps.find(weight.values.data);
         launch_quant_linear(plan.path,
                             {output.rows, plan.channels, plan.reduction, plan.groups.activation, plan.groups.weight},
                             input.values.data, input.scales.ptr<float>(), weight.values.data,
                             weight.scales.ptr<float>(), output.data, workspace.data(), workspace.size(), stream,
-                            format, plan.output_type, finish);
+                            format, plan.output_type, finish, known == weight_maps.end() ? nullptr : &known->second);
     }
 };
 
@@ -59,6 +65,7 @@ QuantizedGemm::QuantizedGemm(cudaStream_t stream, void *, Buffer &workspace, Typ
     if (cudaGetDeviceProperties(&p, workspace.device()) != cudaSuccess)
         throw std::runtime_error("cudaGetDeviceProperties failed");
     impl->multiprocessors = p.multiProcessorCount;
+    impl->chip = ChipModel::b200(p.multiProcessorCount);
     quant_linear_reset_workspace(workspace.data(), workspace.size(), stream);
 }
 QuantizedGemm::~QuantizedGemm() = default;
@@ -85,12 +92,18 @@ void QuantizedGemm::prepare(int rows, int channels, int reduction, Type output_t
     }
     if (impl->sealed) throw std::logic_error("prepared resource missing after initialization");
     KernelProblem problem{rows, channels, reduction, groups.activation, groups.weight};
-    Plan plan{select_tcgen05_path(problem, impl->format, impl->multiprocessors, impl->workspace.size()), rows,
+    Plan plan{select_linear(problem, KernelLimits{false, 0, impl->workspace.size()}, impl->format, impl->chip), rows,
               channels, reduction, output_type, groups};
     if (quant_linear_workspace_bytes(plan.path, problem) > impl->workspace.size())
         throw std::invalid_argument("quantized GEMM workspace too small for this shape");
     ++impl->stats.searches;
     impl->plans.emplace(key, plan);
+}
+void QuantizedGemm::prepare_weight(TensorView values) {
+    if (!values.data || (values.type != Type::I8 && values.type != Type::FP8) || !values.dense()) return;
+    if (impl->weight_maps.count(values.data)) return;
+    if (impl->sealed) throw std::logic_error("prepared resource missing after initialization");
+    impl->weight_maps.emplace(values.data, quant_linear_weight_maps(values.data, values.rows, values.cols));
 }
 void QuantizedGemm::prepare_finish(int rows, int channels, int reduction, Type output_type,
                                    const ops::Epilogue &finish, QuantizationGroups groups) {

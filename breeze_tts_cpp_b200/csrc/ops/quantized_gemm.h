@@ -28,6 +28,9 @@ class QuantizedGemm {
     QuantCacheStats cache_stats() const;
     void prepare(int rows, int output_channels, int input_channels, Type output_type = Type::BF16,
                  QuantizationGroups groups = {});
+    // Addition: builds the TMA descriptor of a quantized weight matrix ahead of time (before seal()),
+    // so that no launch has to encode it. Views that are not one-byte dense matrices are ignored.
+    void prepare_weight(TensorView quantized_values);
     void prepare_finish(int rows, int output_channels, int input_channels, Type output_type,
                         const ops::Epilogue &, QuantizationGroups groups = {});
     void linear(RowScaledView input, RowScaledView weight, TensorView output);

@@ -123,10 +123,12 @@ class Context:
 
     # ---- GEMM
     def prepare_quantized(self, rows: int, channels: int, reduction: int, out_dtype=torch.bfloat16,
-                          groups: tuple[int, int] | None = None) -> tuple[int, int, int, int]:
+                          groups: tuple[int, int] | None = None, weight: RowScaledView | None = None) -> tuple[int, int, int, int]:
         ga, gw = groups if groups is not None else groups_of(self.mode)[:2]
         path = Path_()
         _lib.call("b200q_prepare", self._handle, rows, channels, reduction, _TORCH_TYPES[out_dtype], ga, gw, C.byref(path))
+        if weight is not None:
+            _lib.call("b200q_prepare_weight", self._handle, C.byref(weight.c()))
         return (path.kind, path.tokens, path.channels, path.splits)
 
     def select_path(self, rows, channels, reduction, groups=None):

@@ -8,6 +8,9 @@
  * Conventions (same as the reference's bindings/c_api.cpp:25-40): every call returns 0 on success
  * and -1 on failure, copying a message into `error` (capacity `error_capacity`, may be NULL).
  * All device pointers are borrowed; nothing here allocates at call time except the *_create calls.
+ * Weights and weight scales must be complete on the device (stream-synchronized, or ordered by an
+ * ordinary stream dependency) before the first GEMM that reads them is enqueued: the GEMM kernels
+ * prefetch weight tiles and weight scales ahead of their wait on the preceding kernel.
  * Type codes are the integer values of the reference's tts::Type (src/core/tensor.h:8):
  * BF16=0 F32=1 I32=2 FP8=3 I8=4 F16=5.
  */
@@ -83,6 +86,10 @@ int b200q_quantized_gated(b200q_context *, const b200q_tensor *input, const b200
 int b200q_prepare(b200q_context *, int32_t rows, int32_t output_channels, int32_t input_channels,
                   int32_t output_type, int32_t activation_group, int32_t weight_group, b200q_path *chosen,
                   char *error, size_t error_capacity);
+/* reference: the weight argument of ops::prepare_quantized (src/ops/basic.h:25-26). Builds the TMA
+ * descriptor of a quantized weight matrix once, before b200q_seal, so that launches on that weight
+ * need not encode it. Optional: weights that were never announced still work. */
+int b200q_prepare_weight(b200q_context *, const b200q_row_scaled *weight, char *error, size_t error_capacity);
 /* reference: QuantizedGemm::seal / ops::seal (src/ops/cuda/quantization.h:24). */
 int b200q_seal(b200q_context *, char *error, size_t error_capacity);
 
@@ -134,12 +141,19 @@ int b200q_linear_layer_weight(b200q_linear_layer *, b200q_row_scaled *weight, ch
  * allowed, a host that provides a stream but no workspace): needs no context and no workspace, its
  * 32 KiB of scratch is a device array built into the library. `path` NULL lets the planner choose.
  * Limits: one array per GPU shared by every call, so calls that overlap on the GPU race and each call
- * finds the previous call's contents (the status word is cleared per call); problems needing more
+ * finds the previous call's contents (the status word is cleared per call: read it with
+ * b200q_static_status before the next call); the caller's current device is left unchanged; problems needing more
  * than 32 KiB of scratch are rejected; the first call on a device does one-time set-up and should
  * come before any stream capture. */
 int b200q_quant_linear_static(int32_t device, void *stream, const b200q_path *path, const b200q_row_scaled *input,
                               const b200q_row_scaled *weight, const b200q_tensor *output,
                               const b200q_epilogue *epilogue, char *error, size_t error_capacity);
+
+/* No counterpart in the reference. Status word of the built-in scratch that
+ * b200q_quant_linear_static uses on `device`: waits for `stream`, then returns 0 = clean, nonzero = a
+ * bounded device-side wait gave up during the last static call (its output is invalid). Allocates
+ * nothing. Each static call clears the word before it launches, so ask before the next call. */
+int b200q_static_status(int32_t device, void *stream, int32_t *status, char *error, size_t error_capacity);
 
 /* Blocks until the context's stream is idle and returns the device status word through `status`:
  * 0 = clean; nonzero = a bounded device-side wait gave up (results are invalid). */
@@ -154,6 +168,19 @@ int32_t b200q_row_capacity(int32_t rows, uint32_t bins_per_octave);
 int b200q_plan_path(int32_t rows, int32_t output_channels, int32_t input_channels, int32_t activation_group,
                     int32_t weight_group, int32_t format, int32_t multiprocessors, size_t workspace_bytes,
                     b200q_path *chosen, size_t *workspace_needed, char *error, size_t error_capacity);
+
+/* The launch shapes the kernels accept for a problem — reference: quant_linear_candidates
+ * (src/ops/cuda/quantization_policy.h:27-28). Writes up to `capacity` paths and returns how many
+ * exist (which may exceed `capacity`), or -1 on error. Host only. */
+int b200q_candidates(int32_t rows, int32_t output_channels, int32_t input_channels, int32_t activation_group,
+                     int32_t weight_group, int32_t format, b200q_path *paths, int32_t capacity, char *error,
+                     size_t error_capacity);
+/* The planner's estimate, in microseconds, of one GEMM launch with `path` (fused == 0: plus the row
+ * quantizer before it and a separate finishing pass after it) — reference: linear_pipeline_cost
+ * (src/ops/cuda/quantization_policy.h:30-31). Host only; a negative value reports an error. */
+double b200q_path_cost(int32_t rows, int32_t output_channels, int32_t input_channels, int32_t activation_group,
+                       int32_t weight_group, int32_t format, const b200q_path *path, int32_t multiprocessors,
+                       int32_t gemm_only, char *error, size_t error_capacity);
 
 #ifdef __cplusplus
 }

@@ -77,3 +77,45 @@ def test_context_creation_without_gpu_fails_loudly():
         _lib.call("b200q_context_create", 0, None, None, 0, b"int8", C.byref(handle))
     with pytest.raises(_lib.B200QError):
         _lib.call("b200q_context_create", 0, None, None, 0, b"int4", C.byref(handle))
+
+
+def candidates(rows, n, k, ga=0, gw=0, fmt=I8):
+    paths = (Path_ * 64)()
+    buf = C.create_string_buffer(256)
+    count = _lib.load().b200q_candidates(rows, n, k, ga, gw, fmt, paths, 64, buf, len(buf))
+    assert count >= 0, buf.value
+    return [(p.kind, p.tokens, p.channels, p.splits) for p in paths[:count]]
+
+
+def cost(rows, n, k, path, ga=0, gw=0, fmt=I8, gemm_only=1):
+    buf = C.create_string_buffer(256)
+    value = _lib.load().b200q_path_cost(rows, n, k, ga, gw, fmt, C.byref(Path_(*path)), 148, gemm_only, buf, len(buf))
+    assert value >= 0, buf.value
+    return value
+
+
+def test_candidate_enumeration_and_cost_ranking():
+    """reference interface: quant_linear_candidates / linear_pipeline_cost / select_linear
+    (src/ops/cuda/quantization_policy.h:27-33); here every candidate is a tcgen05 launch shape."""
+    found = candidates(64, 2048, 6144)
+    assert found == [(5, 64, 128, s) for s in range(1, 9)]              # split-K 1..8 = cluster sizes
+    assert candidates(1, 2048, 256) == [(5, 16, 128, 1), (5, 16, 128, 2)]  # never more splits than K blocks
+    assert {p[1] for p in candidates(8192, 4096, 2048)} == {256}
+    assert {p[1] for p in candidates(4096, 2048, 6144, 128, 128)} == {128, 64}
+    assert candidates(16, 2048, 2040) == []                              # K % 16
+    for rows, n, k, ga in ((64, 2048, 6144, 0), (16, 12288, 2048, 0), (4096, 2048, 6144, 128), (300, 640, 1024, 0)):
+        options = candidates(rows, n, k, ga, ga)
+        best = min(options, key=lambda p: (cost(rows, n, k, p, ga, ga), p[3]))
+        chosen, _ = plan(rows, n, k, ga, ga)
+        assert chosen == best                                            # select_linear = cheapest candidate
+        assert cost(rows, n, k, best, ga, ga, gemm_only=0) > cost(rows, n, k, best, ga, ga)
+    # the persistent K-group kernel never splits K: asking for a split selects the split-K kernel instead
+    assert plan(4096, 2048, 6144, 128, 128)[0] == (5, 128, 128, 1)
+
+
+def test_decode_plans_match_the_measured_table():
+    """Splits that were measured fastest on a B200 for the decoder layer's four shapes."""
+    want = {(2048, 4096): 2, (2048, 2048): 4, (2048, 12288): 1, (6144, 2048): 4}
+    for rows in (1, 4, 16, 64):
+        for (k, n), splits in want.items():
+            assert plan(rows, n, k)[0][3] == splits

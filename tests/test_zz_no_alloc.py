@@ -42,7 +42,9 @@ def test_static_entry_matches_regular_entry_twice(oracle, ctx_factory, m, n, k, 
         ep = ops._epilogue(residual_f32=residual)
         _lib.call("b200q_quant_linear_static", 0, None, C.byref(Path_(*path)), C.byref(xv.c()), C.byref(wv.c()),
                   C.byref(ops._tensor(got)), C.byref(ep))
-        torch.cuda.synchronize()
+        status = C.c_int32(-1)
+        _lib.call("b200q_static_status", 0, None, C.byref(status))  # waits for the stream, allocates nothing
+        assert status.value == 0
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f"call {call}"
     # planner-chosen path (path == NULL) gives the same bits as well
     got2 = torch.zeros_like(want)
