@@ -26,7 +26,14 @@ class RowScaled(C.Structure):
 class Epilogue(C.Structure):
     _fields_ = [("bias", Tensor), ("residual", Tensor), ("residual_f32", Tensor), ("value_scale", C.c_float),
                 ("output_scale", C.c_float), ("residual_scale", C.c_float), ("alpha", C.c_float),
-                ("activation", C.c_int32)]
+                ("activation", C.c_int32), ("gate", Tensor), ("condition", Tensor), ("raw", Tensor),
+                ("rows_per_sequence", C.c_int32), ("valid_rows_per_sequence", C.c_int32), ("input_repeat", C.c_int32),
+                ("residual_rows", C.c_void_p)]
+
+
+class NormFusion(C.Structure):
+    _fields_ = [("residual", Tensor), ("projection_bias", Tensor), ("raw", Tensor), ("gate", Tensor), ("shift", Tensor),
+                ("scale", Tensor), ("rows_per_sequence", C.c_int32), ("source_rows", C.c_void_p)]
 
 
 class Path_(C.Structure):
@@ -35,6 +42,7 @@ class Path_(C.Structure):
 
 _ERR = (C.c_char_p, C.c_size_t)
 _PT, _PR, _PE, _PP = C.POINTER(Tensor), C.POINTER(RowScaled), C.POINTER(Epilogue), C.POINTER(Path_)
+_PF = C.POINTER(NormFusion)
 
 # name -> (restype, argtypes); the single source of truth the symbol-export test checks against.
 SIGNATURES = {
@@ -51,11 +59,21 @@ SIGNATURES = {
     "b200q_linear": (C.c_int, (C.c_void_p, _PR, _PR, _PT, _PE, *_ERR)),
     "b200q_quant_linear": (C.c_int, (C.c_void_p, _PP, _PR, _PR, _PT, _PE, *_ERR)),
     "b200q_select_path": (C.c_int, (C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _PP, *_ERR)),
-    "b200q_linear_forward": (C.c_int, (C.c_void_p, _PT, _PR, _PR, _PT, _PE, *_ERR)),
+    "b200q_linear_forward": (C.c_int, (C.c_void_p, _PT, _PR, _PR, _PT, _PE, _PR, *_ERR)),
+    "b200q_pointwise": (C.c_int, (C.c_void_p, _PT, _PT, _PE, *_ERR)),
+    "b200q_pointwise_quantize": (C.c_int, (C.c_void_p, _PT, _PR, _PE, _PT, *_ERR)),
+    "b200q_layer_norm_quantize": (C.c_int, (C.c_void_p, _PT, _PR, _PT, _PT, C.c_float, _PF, _PT, *_ERR)),
+    "b200q_normalized_linear": (C.c_int, (C.c_void_p, _PT, _PR, _PT, _PT, _PT, _PT, _PT, C.c_float, _PF, _PE, _PR,
+                                          C.POINTER(C.c_int32), *_ERR)),
     "b200q_linear_layer_create": (C.c_int, (C.c_void_p, _PT, C.c_int32, _PT, C.POINTER(C.c_void_p), *_ERR)),
     "b200q_linear_layer_destroy": (None, (C.c_void_p,)),
     "b200q_linear_layer_prepare": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, *_ERR)),
     "b200q_linear_layer_forward": (C.c_int, (C.c_void_p, C.c_void_p, _PT, _PT, _PE, _PR, *_ERR)),
+    "b200q_linear_layer_apply": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, _PT, _PT, _PE, *_ERR)),
+    "b200q_linear_layer_forward_segments": (C.c_int, (C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, _PT,
+                                                      C.POINTER(C.c_int32), C.c_int32, _PT, *_ERR)),
+    "b200q_linear_layer_normalized_forward": (C.c_int, (C.c_void_p, C.c_void_p, _PT, _PT, _PT, _PT, _PT, C.c_float, _PF,
+                                                        _PE, _PR, *_ERR)),
     "b200q_linear_layer_weight": (C.c_int, (C.c_void_p, _PR, *_ERR)),
     "b200q_quant_linear_static": (C.c_int, (C.c_int32, C.c_void_p, _PP, _PR, _PR, _PT, _PE, *_ERR)),
     "b200q_static_status": (C.c_int, (C.c_int32, C.c_void_p, C.POINTER(C.c_int32), *_ERR)),

@@ -31,6 +31,9 @@ SOURCES = [
     ("ops/quantization_policy.cpp", []),
     ("ops/context.cpp", []),
     ("ops/ops.cpp", []),
+    ("ops/sequence.cpp", []),
+    ("kernels/sequence_pointwise.cu", ["--fmad=false"]),
+    ("kernels/sequence_norm.cu", ["--fmad=false"]),
     ("layers/linear.cpp", []),
     ("c_api.cpp", []),
 ]

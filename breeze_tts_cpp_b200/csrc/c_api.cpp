@@ -1,6 +1,7 @@
 // extern "C" edge of the library: POD structs in, status code + message out. Exceptions never
 // cross this boundary (same convention as the reference's bindings/c_api.cpp:25-40).
 #include "b200q.h"
+#include "c_api_convert.h"
 #include "kernels/quant_dispatch.h"
 #include "ops/context.h"
 #include "ops/ops.h"
@@ -42,37 +43,11 @@ CudaContext &context_of(b200q_context *c) {
     if (!c || !c->gpu) throw std::invalid_argument("null b200q context");
     return *c->gpu;
 }
-Type type_of(int code) {
-    if (code < 0 || code > int(Type::F64)) throw std::invalid_argument("invalid type code");
-    return static_cast<Type>(code);
-}
-TensorView view_of(const b200q_tensor *t) {
-    if (!t || !t->data) return {};
-    return TensorView(t->data, t->rows, t->cols, type_of(t->type), t->stride, t->device);
-}
-RowScaledView scaled_of(const b200q_row_scaled *r) {
-    if (!r) throw std::invalid_argument("null row-scaled view");
-    RowScaledView v;
-    v.values = view_of(&r->values);
-    v.scales = view_of(&r->scales);
-    v.group_size = r->group_size;
-    v.rotation_size = r->rotation_size;
-    return v;
-}
-ops::Epilogue epilogue_of(const b200q_epilogue *e) {
-    ops::Epilogue out;
-    if (!e) return out;
-    out.bias = view_of(&e->bias);
-    out.residual = view_of(&e->residual);
-    out.residual_f32 = view_of(&e->residual_f32);
-    out.value_scale = e->value_scale;
-    out.output_scale = e->output_scale;
-    out.residual_scale = e->residual_scale;
-    out.alpha = e->alpha;
-    if (e->activation < 0 || e->activation > int(ops::Activation::Sigmoid)) throw std::invalid_argument("invalid activation");
-    out.activation = static_cast<ops::Activation>(e->activation);
-    return out;
-}
+using capi::epilogue_of;
+using capi::fusion_of;
+using capi::scaled_of;
+using capi::type_of;
+using capi::view_of;
 void put_path(b200q_path *out, LinearPath p) {
     if (out) *out = {int32_t(p.kind), p.tokens, p.channels, p.splits};
 }
@@ -192,13 +167,53 @@ int b200q_select_path(b200q_context *c, int32_t rows, int32_t channels, int32_t 
 }
 int b200q_linear_forward(b200q_context *c, const b200q_tensor *input, const b200q_row_scaled *weight,
                          const b200q_row_scaled *scratch, const b200q_tensor *output, const b200q_epilogue *epilogue,
-                         char *error, size_t capacity) {
+                         const b200q_row_scaled *quantized_output, char *error, size_t capacity) {
     return guarded(error, capacity, [&] {
         ExecutionScope scope(context_of(c));
         ops::Epilogue e = epilogue_of(epilogue);
         TensorView bias = e.bias;
         e.bias = {};
-        ops::linear(view_of(input), scaled_of(weight), bias, view_of(output), e, scaled_of(scratch));
+        ops::linear(view_of(input), scaled_of(weight), bias, view_of(output), e, scaled_of(scratch),
+                    quantized_output ? scaled_of(quantized_output) : RowScaledView{});
+    });
+}
+int b200q_pointwise(b200q_context *c, const b200q_tensor *x, const b200q_tensor *y, const b200q_epilogue *epilogue,
+                    char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        ExecutionScope scope(context_of(c));
+        ops::pointwise(view_of(x), view_of(y), epilogue_of(epilogue));
+    });
+}
+int b200q_pointwise_quantize(b200q_context *c, const b200q_tensor *x, const b200q_row_scaled *quantized,
+                             const b200q_epilogue *epilogue, const b200q_tensor *retained, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        ExecutionScope scope(context_of(c));
+        ops::pointwise_quantize(view_of(x), scaled_of(quantized), epilogue_of(epilogue), view_of(retained));
+    });
+}
+int b200q_layer_norm_quantize(b200q_context *c, const b200q_tensor *x, const b200q_row_scaled *quantized,
+                              const b200q_tensor *weight, const b200q_tensor *bias, float epsilon,
+                              const b200q_norm_fusion *fusion, const b200q_tensor *retained, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        ExecutionScope scope(context_of(c));
+        ops::layer_norm_quantize(view_of(x), scaled_of(quantized), view_of(weight), view_of(bias), epsilon,
+                                 fusion_of(fusion), view_of(retained));
+    });
+}
+int b200q_normalized_linear(b200q_context *c, const b200q_tensor *input, const b200q_row_scaled *weight,
+                            const b200q_tensor *bias, const b200q_tensor *normalized, const b200q_tensor *output,
+                            const b200q_tensor *norm_weight, const b200q_tensor *norm_bias, float epsilon,
+                            const b200q_norm_fusion *fusion, const b200q_epilogue *epilogue,
+                            const b200q_row_scaled *quantized_output, int32_t *taken, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        ExecutionScope scope(context_of(c));
+        ops::Epilogue e = epilogue_of(epilogue);
+        if (e.bias.data) throw std::invalid_argument("linear already owns its bias");
+        const bool done = ops::normalized_linear(view_of(input), scaled_of(weight), view_of(bias), view_of(normalized),
+                                                 view_of(output), view_of(norm_weight), view_of(norm_bias), epsilon,
+                                                 fusion_of(fusion), e, nullptr,
+                                                 quantized_output ? scaled_of(quantized_output) : RowScaledView{});
+        if (taken) *taken = done ? 1 : 0;
     });
 }
 int b200q_linear_layer_create(b200q_context *c, const b200q_tensor *parts, int32_t part_count, const b200q_tensor *bias,
@@ -235,6 +250,50 @@ int b200q_linear_layer_forward(b200q_context *c, b200q_linear_layer *l, const b2
         if (e.bias.data) throw std::invalid_argument("linear already owns its bias");
         l->layer->forward(*l->scratch, view_of(input), view_of(output), e,
                           quantized_output ? scaled_of(quantized_output) : RowScaledView{});
+    });
+}
+int b200q_linear_layer_apply(b200q_context *c, b200q_linear_layer *l, int32_t mode, int32_t max_rows, const b200q_tensor *input,
+                             const b200q_tensor *output, const b200q_epilogue *epilogue, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        ExecutionScope scope(context_of(c));
+        if (!l || !l->layer) throw std::invalid_argument("null layer");
+        if (mode < 0 || mode > int(ForwardContext::Execute) || max_rows < 1) throw std::invalid_argument("invalid forward phase");
+        ForwardContext context(1, max_rows, max_rows);
+        context.mode = static_cast<ForwardContext::Mode>(mode);
+        ops::Epilogue e = epilogue_of(epilogue);
+        if (e.bias.data) throw std::invalid_argument("linear already owns its bias");
+        l->layer->forward(view_of(input), view_of(output), context, e);
+    });
+}
+int b200q_linear_layer_forward_segments(b200q_context *c, b200q_linear_layer *l, int32_t mode, int32_t max_rows,
+                                        const b200q_tensor *input, const int32_t *segments, int32_t segment_count,
+                                        const b200q_tensor *output, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        ExecutionScope scope(context_of(c));
+        if (!l || !l->layer) throw std::invalid_argument("null layer");
+        if (mode < 0 || mode > int(ForwardContext::Execute) || max_rows < 1 || segment_count < 0 || (segment_count && !segments))
+            throw std::invalid_argument("invalid forward phase or segments");
+        ForwardContext context(1, max_rows, max_rows);
+        context.mode = static_cast<ForwardContext::Mode>(mode);
+        TensorView ranges = segment_count ? TensorView(const_cast<int32_t *>(segments), segment_count, 3, Type::I32, 0, -1)
+                                          : TensorView::metadata(0, 3, Type::I32, 0, -1);
+        l->layer->forward_segments(view_of(input), ranges, view_of(output), context);
+    });
+}
+int b200q_linear_layer_normalized_forward(b200q_context *c, b200q_linear_layer *l, const b200q_tensor *input,
+                                          const b200q_tensor *normalized, const b200q_tensor *output,
+                                          const b200q_tensor *norm_weight, const b200q_tensor *norm_bias, float epsilon,
+                                          const b200q_norm_fusion *fusion, const b200q_epilogue *epilogue,
+                                          const b200q_row_scaled *quantized_output, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] {
+        ExecutionScope scope(context_of(c));
+        if (!l || !l->layer) throw std::invalid_argument("null layer");
+        if (!l->scratch) throw std::logic_error("layer was not prepared before execution");
+        ops::Epilogue e = epilogue_of(epilogue);
+        if (e.bias.data) throw std::invalid_argument("linear already owns its bias");
+        l->layer->normalized_forward(*l->scratch, view_of(input), view_of(normalized), view_of(output), view_of(norm_weight),
+                                     view_of(norm_bias), epsilon, fusion_of(fusion), e, nullptr,
+                                     quantized_output ? scaled_of(quantized_output) : RowScaledView{});
     });
 }
 int b200q_linear_layer_weight(b200q_linear_layer *l, b200q_row_scaled *weight, char *error, size_t capacity) {

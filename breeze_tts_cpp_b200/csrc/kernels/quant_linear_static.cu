@@ -16,6 +16,7 @@
 //     device address) and should therefore be made before any stream capture begins;
 //   * problems whose scratch need exceeds the array are rejected, nothing is allocated instead.
 #include "b200q.h"
+#include "c_api_convert.h"
 #include "kernels/quant_dispatch.h"
 #include "ops/epilogue.h"
 #include <cstdio>
@@ -77,20 +78,6 @@ class DeviceScope {
     }
 };
 
-TensorView view_of(const b200q_tensor &t) {
-    if (!t.data) return {};
-    if (t.type < 0 || t.type > int(Type::F64)) throw std::invalid_argument("invalid type code");
-    return TensorView(t.data, t.rows, t.cols, static_cast<Type>(t.type), t.stride, t.device);
-}
-RowScaledView scaled_of(const b200q_row_scaled *r) {
-    if (!r) throw std::invalid_argument("null row-scaled view");
-    RowScaledView v;
-    v.values = view_of(r->values);
-    v.scales = view_of(r->scales);
-    v.group_size = r->group_size;
-    v.rotation_size = r->rotation_size;
-    return v;
-}
 } // namespace
 
 extern "C" int b200q_quant_linear_static(int32_t device, void *stream, const b200q_path *path,
@@ -102,8 +89,8 @@ extern "C" int b200q_quant_linear_static(int32_t device, void *stream, const b20
         DeviceScope current(device);
         const DeviceScratch on_device = scratch_of(device);
         void *scratch = on_device.address;
-        RowScaledView x = scaled_of(input), w = scaled_of(weight);
-        TensorView y = view_of(*output);
+        RowScaledView x = capi::scaled_of(input), w = capi::scaled_of(weight);
+        TensorView y = capi::view_of(output);
         x.validate();
         w.validate();
         if (x.values.type != w.values.type || x.values.cols != w.values.cols || x.rotation_size != w.rotation_size ||
@@ -118,18 +105,7 @@ extern "C" int b200q_quant_linear_static(int32_t device, void *stream, const b20
         if (need > kStaticScratchBytes)
             throw std::invalid_argument("this problem needs " + std::to_string(need) + " bytes of scratch; the built-in scratch holds " +
                                         std::to_string(kStaticScratchBytes) + " and this entry point never allocates");
-        ops::Epilogue finish;
-        if (epilogue) {
-            finish.bias = view_of(epilogue->bias);
-            finish.residual = view_of(epilogue->residual);
-            finish.residual_f32 = view_of(epilogue->residual_f32);
-            finish.value_scale = epilogue->value_scale;
-            finish.output_scale = epilogue->output_scale;
-            finish.residual_scale = epilogue->residual_scale;
-            finish.alpha = epilogue->alpha;
-            if (epilogue->activation < 0 || epilogue->activation > int(ops::Activation::Sigmoid)) throw std::invalid_argument("invalid activation");
-            finish.activation = static_cast<ops::Activation>(epilogue->activation);
-        }
+        const ops::Epilogue finish = capi::epilogue_of(epilogue);
         auto s = static_cast<cudaStream_t>(stream);
         // The shared array still holds whatever the previous call left; the GEMM expects its header
         // (status word included) to start at zero, so clear it on the stream ahead of the launch.

@@ -1,12 +1,13 @@
 // Quantized Linear layer: holds a RowScaledView weight (+ optional bias) and runs
 // quantize -> GEMM -> fused epilogue through the op layer. Public methods follow the reference's
 // `tts::Linear` (src/layers/linear.h:11-76) for the quantized case; construction from a checkpoint
-// (`Weights`) and the `ForwardContext` plumbing are the reference engine's own and are replaced
-// here by `Linear::quantize`, which performs the load-time step of `Weights::quantized`
+// (`Weights`) is the reference engine's own and is replaced here by `Linear::quantize`, which
+// performs the load-time step of `Weights::quantized`
 // (src/io/weights.cpp:80-87,133-154): concatenate the source matrices by rows and quantize them
 // on the device into storage the layer owns.
 #pragma once
 #include "core/buffer.h"
+#include "core/forward_context.h"
 #include "layers/quantization.h"
 #include "ops/ops.h"
 #include <memory>
@@ -47,5 +48,34 @@ class Linear {
     // quantized_output the finished rows are re-quantized for the next layer.
     void forward(Workspace &workspace, TensorView input, TensorView output, ops::Epilogue epilogue = {},
                  RowScaledView quantized_output = {}) const;
+    void project(Workspace &workspace, TensorView input, TensorView output) const; // no bias, no epilogue
+
+    // Phase-switched calls (reference: src/layers/linear.cpp:49-88): Prepare plans every row class up to
+    // context.max_rows and sizes the layer's own activation scratch; Execute runs; Plan and Capture
+    // launch nothing. The first form takes its output from the context's scratch arena.
+    TensorView forward(TensorView input, ForwardContext &context, const ops::Epilogue &finish = {}) const;
+    TensorView forward(TensorView input, TensorView output, ForwardContext &context, const ops::Epilogue &finish = {}) const;
+    TensorView project(TensorView input, TensorView output, ForwardContext &context) const;
+    // `segments` is a host I32 [S, 3] list of (first input row, row count, first output row); zero
+    // segments or one contiguous cover runs the whole batch at once (reference: linear.cpp:89-121).
+    TensorView forward_segments(TensorView input, TensorView segments, TensorView output, ForwardContext &context) const;
+
+    // LayerNorm of the input fused with its quantization into the workspace (reference: linear.cpp:177-185).
+    RowScaledView normalize_input(Workspace &workspace, TensorView input, TensorView norm_weight, TensorView norm_bias,
+                                  float epsilon, const ops::NormFusion &fusion, TensorView retained = {}) const;
+    // LayerNorm + projection: one fused launch when the shape allows it, else normalize_input followed
+    // by the projection (reference: linear.cpp:195-214). Always true for a quantized layer without write-back.
+    bool normalized_forward(Workspace &workspace, TensorView input, TensorView normalized, TensorView output,
+                            TensorView norm_weight, TensorView norm_bias, float epsilon, const ops::NormFusion &fusion,
+                            ops::Epilogue epilogue = {}, const QkvProjectionOutput *writeback = nullptr,
+                            RowScaledView quantized_output = {}) const;
+
+  private:
+    TensorView apply_context(TensorView input, TensorView output, ForwardContext &context, TensorView bias,
+                             const ops::Epilogue &finish) const;
+    void validate_types(TensorView input, TensorView output) const;
+    Workspace &context_workspace(const ForwardContext &context) const;
+    mutable std::shared_ptr<Workspace> context_workspace_; // made in Prepare, reused by every Execute
+    mutable int context_rows_ = 0;
 };
 } // namespace tts

@@ -22,13 +22,25 @@ struct Epilogue {
     int rows_per_sequence = 1;
     int valid_rows_per_sequence = 0;
     int input_repeat = 1;
-    const int *residual_rows = nullptr;
+    const int *residual_rows = nullptr; // index into residual rows; negative entries contribute zero
+    // Indirect addressing of the reference's packed-sequence consumers. No operator of this library
+    // takes them: they are kept so that an Epilogue is built the same way, and rejected when set.
+    const struct SequenceLayout *packed = nullptr;
+    const void *const *condition_sources = nullptr;
+    void *const *output_rows = nullptr;
     TensorView residual_f32; // extension: fp32 [rows, channels], added in fp32 before rounding
 };
 
 // True when the GEMM's own epilogue can apply the whole description (no second pass needed).
 inline bool fusable(const Epilogue &e) {
     return !e.raw.data && !e.gate.data && !e.condition.data && !e.valid_rows_per_sequence &&
-           e.input_repeat == 1 && !e.residual_rows && e.activation != Activation::Mish;
+           e.input_repeat == 1 && !e.residual_rows && e.activation != Activation::Mish && !e.packed &&
+           !e.condition_sources && !e.output_rows;
+}
+// True when nothing at all follows the projection.
+inline bool plain(const Epilogue &e) {
+    return !e.bias.data && !e.residual.data && !e.residual_f32.data && !e.gate.data && !e.condition.data &&
+           !e.raw.data && e.activation == Activation::Identity && e.value_scale == 1 && e.output_scale == 1 &&
+           !e.valid_rows_per_sequence && !e.packed && !e.condition_sources && !e.output_rows;
 }
 } // namespace tts::ops

@@ -48,7 +48,9 @@ void seal(int device) {
 }
 
 // reference: src/ops/linear.cpp:26-83, quantized-weight branch. The dense BF16 branch of the
-// reference is a different subsystem and is not provided here.
+// reference is a different subsystem and is not provided here. An epilogue the GEMM can apply rides
+// in its own epilogue; any other legal epilogue runs as the separate finishing pass the reference
+// uses (src/ops/linear.cpp:76-82), fused with the re-quantization when `quantized_output` is asked for.
 void linear(const LinearOperand &input, const LinearOperand &weight, TensorView bias, TensorView output, Epilogue e,
             RowScaledView scratch, RowScaledView quantized_output) {
     auto &gpu = execution_context(output, {bias, e.residual, e.gate, e.condition, e.raw, e.residual_f32,
@@ -62,6 +64,7 @@ void linear(const LinearOperand &input, const LinearOperand &weight, TensorView 
         if (source.overlaps(output))
             throw std::invalid_argument("linear epilogue source aliases its projection output");
     e.bias = bias;
+    if (quantized_output.values.data) validate_pointwise_quantize(output, quantized_output, e);
     matrix->validate();
     RowScaledView activation;
     if (const auto *dense = std::get_if<TensorView>(&input)) {
@@ -73,12 +76,55 @@ void linear(const LinearOperand &input, const LinearOperand &weight, TensorView 
     if (activation.values.cols != matrix->values.cols || output.rows != activation.values.rows ||
         output.cols != matrix->values.rows || !output.dense())
         throw std::invalid_argument("quantized linear dimensions/layout mismatch");
-    const bool plain = !e.bias.data && !e.residual.data && !e.residual_f32.data && !e.gate.data &&
-                       !e.condition.data && !e.raw.data && e.activation == Activation::Identity &&
-                       e.value_scale == 1 && e.output_scale == 1 && !e.valid_rows_per_sequence;
-    if (plain) gpu.quantization->linear(activation, *matrix, output);
-    else if (!gpu.quantization->linear_finish(activation, *matrix, output, e))
-        throw std::invalid_argument("epilogue cannot be fused into the quantized GEMM in this build");
-    if (quantized_output.values.data) quantize_rows(output, quantized_output);
+    if (plain(e)) {
+        gpu.quantization->linear(activation, *matrix, output);
+        if (quantized_output.values.data) quantize_rows(output, quantized_output);
+        return;
+    }
+    if (gpu.quantization->linear_finish(activation, *matrix, output, e)) {
+        if (quantized_output.values.data) quantize_rows(output, quantized_output);
+        return;
+    }
+    if (e.residual_f32.data) throw std::invalid_argument("an fp32 residual needs an epilogue the GEMM can fuse");
+    gpu.quantization->linear(activation, *matrix, output);
+    if (quantized_output.values.data) pointwise_quantize(output, quantized_output, e, {}, gpu.multiprocessors);
+    else pointwise(output, output, e);
+}
+
+// reference: ops::normalized_linear, src/ops/linear.cpp:84-126 (quantized-weight branch).
+bool normalized_linear(TensorView input, const LinearOperand &weight, TensorView bias, TensorView normalized,
+                       TensorView output, TensorView norm_weight, TensorView norm_bias, float epsilon,
+                       const NormFusion &fusion, Epilogue e, const QkvProjectionOutput *writeback,
+                       RowScaledView quantized_output) {
+    auto &gpu = execution_context(input, {bias, normalized, output, norm_weight, norm_bias, fusion.residual,
+                                          fusion.projection_bias, fusion.raw, fusion.gate, fusion.shift, fusion.scale,
+                                          e.residual, e.gate, e.condition, e.raw, quantized_output.values,
+                                          quantized_output.scales});
+    if (e.bias.data) throw std::invalid_argument("linear already owns its bias");
+    for (const TensorView &source : {bias, e.residual, e.gate, e.condition})
+        if (source.overlaps(output))
+            throw std::invalid_argument("linear epilogue source aliases its projection output");
+    if (e.packed || e.condition_sources || e.output_rows) return false;
+    const auto *quantized = std::get_if<RowScaledView>(&weight);
+    if (!quantized) throw std::invalid_argument("this library only executes quantized weights");
+    if (!gpu.quantization) throw std::logic_error("context was created without a quantization mode");
+    if (writeback) return false; // the fused Q/K/V cache write-back belongs to the attention subsystem
+    auto project = [&](const Epilogue &epilogue) {
+        return gpu.quantization->normalized_linear(input, normalized, norm_weight, norm_bias, epsilon, fusion, *quantized,
+                                                   output, epilogue, {}, nullptr);
+    };
+    if (quantized_output.values.data) {
+        e.bias = bias;
+        validate_pointwise_quantize(output, quantized_output, e);
+        if (quantized_output.values.type == quantized->values.type && project(e)) {
+            quantize_rows(output, quantized_output);
+        } else {
+            if (!project({})) return false;
+            pointwise_quantize(output, quantized_output, e, {}, gpu.multiprocessors);
+        }
+        return true;
+    }
+    e.bias = bias;
+    return project(e);
 }
 } // namespace tts::ops

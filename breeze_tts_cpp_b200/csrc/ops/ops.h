@@ -3,8 +3,12 @@
 #pragma once
 #include "core/quantization.h"
 #include "ops/epilogue.h"
+#include "ops/sequence.h"
 #include <variant>
 
+namespace tts {
+struct QkvProjectionOutput;
+}
 namespace tts::ops {
 using LinearOperand = std::variant<TensorView, RowScaledView>;
 
@@ -24,5 +28,12 @@ void quantized_gated(TensorView input, RowScaledView output, int kind);
 // for the next layer and `output` is scratch.
 void linear(const LinearOperand &input, const LinearOperand &weight, TensorView bias, TensorView output,
             Epilogue = {}, RowScaledView scratch = {}, RowScaledView quantized_output = {});
+// LayerNorm + quantize + projection + finish in one launch for narrow rows (K <= 512, per-row scales).
+// False means "not taken": the caller runs layer_norm_quantize + linear instead, exactly as with the
+// reference (src/ops/linear.h:15-18). The attention write-back argument is accepted and declined.
+bool normalized_linear(TensorView input, const LinearOperand &weight, TensorView bias, TensorView normalized,
+                       TensorView output, TensorView norm_weight, TensorView norm_bias, float epsilon,
+                       const NormFusion &fusion, Epilogue = {}, const QkvProjectionOutput *writeback = nullptr,
+                       RowScaledView quantized_output = {});
 void seal(int device);
 } // namespace tts::ops

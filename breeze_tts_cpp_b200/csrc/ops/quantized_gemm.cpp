@@ -1,7 +1,9 @@
 #include "ops/quantized_gemm.h"
 #include "kernels/quant_dispatch.h"
+#include "kernels/sequence_pointwise.h"
 #include "ops/epilogue.h"
 #include "ops/quantization_policy.h"
+#include "ops/sequence.h"
 #include <map>
 #include <tuple>
 
@@ -128,10 +130,55 @@ bool QuantizedGemm::linear_finish(RowScaledView input, RowScaledView weight, Ten
     impl->run(*plan, input, weight, output, &finish);
     return true;
 }
-bool QuantizedGemm::normalized_linear(TensorView, TensorView, TensorView, TensorView, float, const ops::NormFusion &,
-                                      RowScaledView, TensorView, const ops::Epilogue &, RowScaledView,
-                                      const QkvProjectionOutput *) {
-    return false;
+// reference: QuantizedGemm::normalized_linear (src/ops/cuda/quantization.cpp:479-494) in front of
+// normalized_quantized_linear (src/ops/kernels/sequence/sequence_norm.cu:518-575): every condition
+// under which that kernel declines returns false here too.
+bool QuantizedGemm::normalized_linear(TensorView x, TensorView normalized, TensorView norm_weight, TensorView norm_bias,
+                                      float epsilon, const ops::NormFusion &f, RowScaledView weight, TensorView output,
+                                      const ops::Epilogue &e, RowScaledView encoded, const QkvProjectionOutput *writeback) {
+    if (writeback || e.packed || e.condition_sources || e.output_rows || weight.group_size || encoded.group_size ||
+        weight.rotation_size || encoded.rotation_size)
+        return false;
+    weight.validate();
+    const int n = weight.values.rows, k = weight.values.cols;
+    if (weight.values.type != impl->format || !x.data || !weight.values.data || !weight.scales.data || !output.data ||
+        x.rows < 1 || x.rows > 65535 || n < 1 || k < 4 || k % 4 || reinterpret_cast<uintptr_t>(weight.values.data) % 4 ||
+        k > 512 || x.cols != k || (x.type != Type::F16 && x.type != Type::BF16) || output.type != x.type ||
+        output.rows != x.rows || output.cols != n || f.source_rows ||
+        (normalized.data && (normalized.rows != x.rows || normalized.cols != k || normalized.type != x.type)) ||
+        (e.activation != ops::Activation::Identity && e.activation != ops::Activation::Relu) || e.residual.data ||
+        e.residual_f32.data || e.gate.data || e.condition.data || e.raw.data || e.residual_rows || e.input_repeat != 1 ||
+        e.value_scale != 1 || e.output_scale != 1 || !(epsilon > 0))
+        return false;
+    for (const TensorView &source : {x, f.residual, f.projection_bias, f.gate, f.scale, f.shift, norm_weight, norm_bias,
+                                     weight.values, weight.scales, e.bias})
+        if (normalized.overlaps(source) || output.overlaps(source) || f.raw.overlaps(source)) return false;
+    if (normalized.overlaps(output) || f.raw.overlaps(output) || f.raw.overlaps(normalized)) return false;
+    auto vector_of = [&](const TensorView &v) { return !v.data || (v.type == x.type && v.numel() == size_t(k)); };
+    auto rows_of = [&](const TensorView &v) { return !v.data || (v.type == x.type && v.rows == x.rows && v.cols == k); };
+    if (!vector_of(norm_weight) || !vector_of(norm_bias) || !vector_of(f.projection_bias) || !rows_of(f.residual) ||
+        !rows_of(f.raw) || f.rows_per_sequence < 1 || x.rows % f.rows_per_sequence)
+        throw std::invalid_argument("sequence operation shape/type mismatch");
+    for (const TensorView *v : {&f.gate, &f.shift, &f.scale})
+        if (v->data && (v->type != x.type || v->cols != k || (v->rows != 1 && v->rows != x.rows / f.rows_per_sequence)))
+            throw std::invalid_argument("invalid normalization modulation");
+    if (e.bias.data && (e.bias.type != x.type || e.bias.numel() != size_t(n)))
+        throw std::invalid_argument("sequence operation shape/type mismatch");
+    if (e.rows_per_sequence < 1 || x.rows % e.rows_per_sequence || e.valid_rows_per_sequence < 0 ||
+        e.valid_rows_per_sequence > e.rows_per_sequence)
+        throw std::invalid_argument("invalid epilogue sequence length");
+    if (encoded.values.data || encoded.scales.data) {
+        encoded.validate();
+        if (encoded.values.type != weight.values.type || encoded.values.rows != x.rows || encoded.values.cols != k)
+            throw std::invalid_argument("normalized projection quantized output mismatch");
+        for (const TensorView &source : {x, normalized, norm_weight, norm_bias, f.residual, f.projection_bias, f.raw, f.gate,
+                                         f.shift, f.scale, weight.values, weight.scales, output, e.bias})
+            if (encoded.values.overlaps(source) || encoded.scales.overlaps(source))
+                throw std::invalid_argument("quantized output overlaps sequence storage");
+    }
+    launch_normalized_quantized_linear(x, normalized, norm_weight, norm_bias, epsilon, f, weight, output, e, encoded,
+                                       impl->stream);
+    return true;
 }
 LinearPath QuantizedGemm::planned_path(int rows, int channels, int reduction, Type output_type,
                                        QuantizationGroups groups) const {

@@ -36,8 +36,8 @@ class QuantizedGemm {
     void linear(RowScaledView input, RowScaledView weight, TensorView output);
     // True when the epilogue ran inside the GEMM; false leaves it to the caller's separate pass.
     bool linear_finish(RowScaledView input, RowScaledView weight, TensorView output, const ops::Epilogue &);
-    // The fused norm+quantize+projection kernel for K <= 512 is not part of this build: always false,
-    // which by contract leaves the caller's two-step path responsible.
+    // Fused LayerNorm + quantize + projection for K <= 512 with per-row scales; false = not taken, which
+    // by contract leaves the caller's two-step path responsible.
     bool normalized_linear(TensorView input, TensorView normalized, TensorView norm_weight,
                            TensorView norm_bias, float epsilon, const ops::NormFusion &,
                            RowScaledView weight, TensorView output, const ops::Epilogue &,

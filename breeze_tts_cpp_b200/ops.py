@@ -14,7 +14,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib
-from ._lib import BF16, F16, F32, FP8, I8, I32, Epilogue, Path_, RowScaled, Tensor
+from ._lib import BF16, F16, F32, FP8, I8, I32, Epilogue, NormFusion, Path_, RowScaled, Tensor
 
 MODES = ("int8", "fp8", "group_int8", "group_fp8")
 _TORCH_TYPES = {torch.bfloat16: BF16, torch.float16: F16, torch.float32: F32, torch.int32: I32,
@@ -73,9 +73,21 @@ class RowScaledView:
 
 
 def _epilogue(bias=None, residual=None, residual_f32=None, activation=0, value_scale=1.0, output_scale=1.0,
-              residual_scale=1.0, alpha=0.1) -> Epilogue:
+              residual_scale=1.0, alpha=0.1, gate=None, condition=None, raw=None, rows_per_sequence=1,
+              valid_rows_per_sequence=0, input_repeat=1, residual_rows=None) -> Epilogue:
+    """reference: ops::Epilogue (src/ops/sequence.h:8-27); residual_rows is a device int32 tensor."""
+    rows_ptr = C.c_void_p(residual_rows.data_ptr()) if residual_rows is not None else None
     return Epilogue(_tensor(bias), _tensor(residual), _tensor(residual_f32, F32), value_scale, output_scale,
-                    residual_scale, alpha, activation)
+                    residual_scale, alpha, activation, _tensor(gate), _tensor(condition), _tensor(raw), rows_per_sequence,
+                    valid_rows_per_sequence, input_repeat, rows_ptr)
+
+
+def _fusion(residual=None, projection_bias=None, raw=None, gate=None, shift=None, scale=None, rows_per_sequence=1,
+            source_rows=None) -> NormFusion:
+    """reference: ops::NormFusion (src/ops/sequence.h:53-57); source_rows is a device int32 tensor."""
+    rows_ptr = C.c_void_p(source_rows.data_ptr()) if source_rows is not None else None
+    return NormFusion(_tensor(residual), _tensor(projection_bias), _tensor(raw), _tensor(gate), _tensor(shift),
+                      _tensor(scale), rows_per_sequence, rows_ptr)
 
 
 class Context:
@@ -151,11 +163,42 @@ class Context:
                   C.byref(_tensor(out)), ep)
         return out
 
-    def linear(self, x: torch.Tensor, w: RowScaledView, scratch: RowScaledView, out: torch.Tensor, **epilogue):
+    def linear(self, x: torch.Tensor, w: RowScaledView, scratch: RowScaledView, out: torch.Tensor,
+               quantized_output: RowScaledView | None = None, **epilogue):
         ep = C.byref(_epilogue(**epilogue)) if epilogue else None
+        qo = C.byref(quantized_output.c()) if quantized_output is not None else None
         _lib.call("b200q_linear_forward", self._handle, C.byref(_tensor(x)), C.byref(w.c()), C.byref(scratch.c()),
-                  C.byref(_tensor(out)), ep)
+                  C.byref(_tensor(out)), ep, qo)
         return out
+
+    # ---- row-wise operators around the projections
+    def pointwise(self, x: torch.Tensor, y: torch.Tensor, **epilogue) -> torch.Tensor:
+        _lib.call("b200q_pointwise", self._handle, C.byref(_tensor(x)), C.byref(_tensor(y)), C.byref(_epilogue(**epilogue)))
+        return y
+
+    def pointwise_quantize(self, x: torch.Tensor, out: RowScaledView, retained: torch.Tensor | None = None,
+                           **epilogue) -> RowScaledView:
+        _lib.call("b200q_pointwise_quantize", self._handle, C.byref(_tensor(x)), C.byref(out.c()),
+                  C.byref(_epilogue(**epilogue)), C.byref(_tensor(retained)))
+        return out
+
+    def layer_norm_quantize(self, x: torch.Tensor, out: RowScaledView, weight=None, bias=None, epsilon: float = 1e-5,
+                            retained: torch.Tensor | None = None, **fusion) -> RowScaledView:
+        _lib.call("b200q_layer_norm_quantize", self._handle, C.byref(_tensor(x)), C.byref(out.c()), C.byref(_tensor(weight)),
+                  C.byref(_tensor(bias)), epsilon, C.byref(_fusion(**fusion)), C.byref(_tensor(retained)))
+        return out
+
+    def normalized_linear(self, x: torch.Tensor, w: RowScaledView, out: torch.Tensor, norm_weight=None, norm_bias=None,
+                          epsilon: float = 1e-5, bias=None, normalized=None, fusion: dict | None = None,
+                          quantized_output: RowScaledView | None = None, **epilogue) -> bool:
+        """True when the fused kernel ran; False leaves the two-step path to the caller."""
+        taken = C.c_int32(0)
+        qo = C.byref(quantized_output.c()) if quantized_output is not None else None
+        _lib.call("b200q_normalized_linear", self._handle, C.byref(_tensor(x)), C.byref(w.c()), C.byref(_tensor(bias)),
+                  C.byref(_tensor(normalized)), C.byref(_tensor(out)), C.byref(_tensor(norm_weight)),
+                  C.byref(_tensor(norm_bias)), epsilon, C.byref(_fusion(**(fusion or {}))), C.byref(_epilogue(**epilogue)),
+                  qo, C.byref(taken))
+        return bool(taken.value)
 
     def status(self) -> int:
         value = C.c_int32(0)
@@ -186,6 +229,32 @@ class Linear:
         ep = C.byref(_epilogue(**epilogue)) if epilogue else None
         qo = C.byref(quantized_output.c()) if quantized_output is not None else None
         _lib.call("b200q_linear_layer_forward", self.ctx._handle, self._handle, C.byref(_tensor(x)), C.byref(_tensor(out)), ep, qo)
+        return out
+
+    PLAN, PREPARE, CAPTURE, EXECUTE = 0, 1, 2, 3  # reference: ForwardContext::Mode (src/core/forward_context.h:58)
+
+    def apply(self, mode: int, max_rows: int, x: torch.Tensor, out: torch.Tensor, **epilogue) -> torch.Tensor:
+        """Phase-switched forward (reference: Linear::forward(input, output, ForwardContext &, finish))."""
+        ep = C.byref(_epilogue(**epilogue)) if epilogue else None
+        _lib.call("b200q_linear_layer_apply", self.ctx._handle, self._handle, mode, max_rows, C.byref(_tensor(x)),
+                  C.byref(_tensor(out)), ep)
+        return out
+
+    def forward_segments(self, mode: int, max_rows: int, x: torch.Tensor, segments: list[tuple[int, int, int]],
+                         out: torch.Tensor) -> torch.Tensor:
+        flat = (C.c_int32 * (3 * len(segments)))(*[v for s in segments for v in s]) if segments else None
+        _lib.call("b200q_linear_layer_forward_segments", self.ctx._handle, self._handle, mode, max_rows, C.byref(_tensor(x)),
+                  flat, len(segments), C.byref(_tensor(out)))
+        return out
+
+    def normalized_forward(self, x: torch.Tensor, out: torch.Tensor, norm_weight=None, norm_bias=None, epsilon: float = 1e-5,
+                           normalized=None, fusion: dict | None = None, quantized_output: RowScaledView | None = None,
+                           **epilogue) -> torch.Tensor:
+        ep = C.byref(_epilogue(**epilogue)) if epilogue else None
+        qo = C.byref(quantized_output.c()) if quantized_output is not None else None
+        _lib.call("b200q_linear_layer_normalized_forward", self.ctx._handle, self._handle, C.byref(_tensor(x)),
+                  C.byref(_tensor(normalized)), C.byref(_tensor(out)), C.byref(_tensor(norm_weight)),
+                  C.byref(_tensor(norm_bias)), epsilon, C.byref(_fusion(**(fusion or {}))), ep, qo)
         return out
 
     def weight(self) -> RowScaled:

@@ -37,14 +37,33 @@ typedef struct b200q_row_scaled {
     int32_t group_size, rotation_size;
 } b200q_row_scaled;
 
-/* reference: tts::ops::Epilogue (src/ops/sequence.h:8-27), the fusable subset, plus the fp32
- * residual of the synthetic decode workload. activation uses ops::Activation codes
- * (src/ops/activation.h:4): 0 identity, 1 relu, 2 leaky relu, 3 silu, 4 gelu, 5 gelu-tanh, 7 tanh, 8 sigmoid. */
+/* reference: tts::ops::Epilogue (src/ops/sequence.h:8-27), plus the fp32 residual of the synthetic
+ * decode workload. activation uses ops::Activation codes (src/ops/activation.h:4): 0 identity, 1 relu,
+ * 2 leaky relu, 3 silu, 4 gelu, 5 gelu-tanh, 6 mish, 7 tanh, 8 sigmoid. gate and condition are
+ * [1, N] or [sequences, N]; raw receives the pre-activation value; rows past
+ * valid_rows_per_sequence inside each sequence of rows_per_sequence rows are zeroed (0 = no masking);
+ * residual_rows (device int32 per output row, negative = no residual) indexes the residual rows;
+ * input_repeat > 1 reads input row r / input_repeat (finishing passes only). Zero-initialise the
+ * struct and set value_scale = output_scale = residual_scale = 1, rows_per_sequence = input_repeat = 1.
+ * bias, residual, residual_f32, the scales and activations 0-5,7,8 ride inside the GEMM; everything
+ * else runs as a separate finishing pass, as in the reference (src/ops/linear.cpp:76-82). */
 typedef struct b200q_epilogue {
     b200q_tensor bias, residual, residual_f32;
     float value_scale, output_scale, residual_scale, alpha;
     int32_t activation;
+    b200q_tensor gate, condition, raw;
+    int32_t rows_per_sequence, valid_rows_per_sequence, input_repeat;
+    const int32_t *residual_rows;
 } b200q_epilogue;
+
+/* reference: tts::ops::NormFusion (src/ops/sequence.h:53-57): what is added to a row before
+ * LayerNorm (projection bias, gate, residual; raw keeps that sum) and the per-sequence modulation
+ * applied after it (scale, shift). source_rows (device int32 per output row) gathers input rows. */
+typedef struct b200q_norm_fusion {
+    b200q_tensor residual, projection_bias, raw, gate, shift, scale;
+    int32_t rows_per_sequence;
+    const int32_t *source_rows;
+} b200q_norm_fusion;
 
 /* reference: tts::LinearPath (src/ops/kernels/quant/kernel_config.h:5-9). kind 5 = tcgen05. */
 typedef struct b200q_path {
@@ -111,10 +130,36 @@ int b200q_select_path(b200q_context *, int32_t rows, int32_t output_channels, in
                       size_t error_capacity);
 
 /* reference: ops::linear with a dense activation (src/ops/linear.h:11-14): quantize `input` into
- * `scratch`, run the GEMM with bias/epilogue fused. */
+ * `scratch`, run the GEMM with the epilogue fused where it can be and as a finishing pass where it
+ * cannot; with `quantized_output` (may be NULL) the finished rows are also quantized for the next
+ * projection. */
 int b200q_linear_forward(b200q_context *, const b200q_tensor *input, const b200q_row_scaled *weight,
                          const b200q_row_scaled *scratch, const b200q_tensor *output,
-                         const b200q_epilogue *epilogue, char *error, size_t error_capacity);
+                         const b200q_epilogue *epilogue, const b200q_row_scaled *quantized_output, char *error,
+                         size_t error_capacity);
+
+/* reference: ops::pointwise (src/ops/sequence.h:35): y = finish(x) as a pass of its own; x may be y. */
+int b200q_pointwise(b200q_context *, const b200q_tensor *x, const b200q_tensor *y, const b200q_epilogue *epilogue,
+                    char *error, size_t error_capacity);
+/* reference: ops::pointwise_quantize (src/ops/sequence.h:36-41): finish(x), rounded to x's type,
+ * optionally kept in `retained` (may be NULL), quantized in the same pass. */
+int b200q_pointwise_quantize(b200q_context *, const b200q_tensor *x, const b200q_row_scaled *quantized,
+                             const b200q_epilogue *epilogue, const b200q_tensor *retained, char *error,
+                             size_t error_capacity);
+/* reference: ops::layer_norm_quantize (src/ops/sequence.h:60-63). weight, bias, fusion, retained may
+ * be NULL / have data == NULL. Rows of up to 8192 columns. */
+int b200q_layer_norm_quantize(b200q_context *, const b200q_tensor *x, const b200q_row_scaled *quantized,
+                              const b200q_tensor *weight, const b200q_tensor *bias, float epsilon,
+                              const b200q_norm_fusion *fusion, const b200q_tensor *retained, char *error,
+                              size_t error_capacity);
+/* reference: ops::normalized_linear over a quantized weight (src/ops/linear.h:15-18): LayerNorm +
+ * quantize + projection + bias/ReLU in one launch when K <= 512 with per-row scales. *taken = 0 means
+ * the fused kernel declined (nothing was launched) and the caller runs the two-step path. */
+int b200q_normalized_linear(b200q_context *, const b200q_tensor *input, const b200q_row_scaled *weight,
+                            const b200q_tensor *bias, const b200q_tensor *normalized, const b200q_tensor *output,
+                            const b200q_tensor *norm_weight, const b200q_tensor *norm_bias, float epsilon,
+                            const b200q_norm_fusion *fusion, const b200q_epilogue *epilogue,
+                            const b200q_row_scaled *quantized_output, int32_t *taken, char *error, size_t error_capacity);
 
 /* ---- Linear layer object --------------------------------------------------------------------
  * reference: tts::Linear (src/layers/linear.h:11-76) over a quantized weight, with the load-time
@@ -133,6 +178,26 @@ int b200q_linear_layer_prepare(b200q_context *, b200q_linear_layer *, int32_t ma
 int b200q_linear_layer_forward(b200q_context *, b200q_linear_layer *, const b200q_tensor *input, const b200q_tensor *output,
                                const b200q_epilogue *epilogue, const b200q_row_scaled *quantized_output, char *error,
                                size_t error_capacity);
+/* reference: Linear::forward(input, output, ForwardContext &, finish) and its phase switch
+ * (src/layers/linear.cpp:49-76): mode 0 Plan and 2 Capture launch nothing, 1 Prepare plans every row
+ * class up to max_rows and sizes the layer's activation scratch (before b200q_seal), 3 Execute runs
+ * quantize -> GEMM -> epilogue and allocates nothing. */
+int b200q_linear_layer_apply(b200q_context *, b200q_linear_layer *, int32_t mode, int32_t max_rows, const b200q_tensor *input,
+                             const b200q_tensor *output, const b200q_epilogue *epilogue, char *error, size_t error_capacity);
+/* reference: Linear::forward_segments (src/layers/linear.cpp:89-121). `segments` is a HOST array of
+ * segment_count triples (first input row, row count, first output row). Same modes as above. */
+int b200q_linear_layer_forward_segments(b200q_context *, b200q_linear_layer *, int32_t mode, int32_t max_rows,
+                                        const b200q_tensor *input, const int32_t *segments, int32_t segment_count,
+                                        const b200q_tensor *output, char *error, size_t error_capacity);
+/* reference: Linear::normalized_forward with a workspace (src/layers/linear.cpp:195-214): LayerNorm of
+ * the input fused with the projection (one launch when K <= 512 with per-row scales, else LayerNorm +
+ * quantize followed by the GEMM). normalized, norm_bias, fusion, epilogue, quantized_output may be NULL.
+ * The layer must have been prepared (b200q_linear_layer_prepare) for at least input->rows rows. */
+int b200q_linear_layer_normalized_forward(b200q_context *, b200q_linear_layer *, const b200q_tensor *input,
+                                          const b200q_tensor *normalized, const b200q_tensor *output,
+                                          const b200q_tensor *norm_weight, const b200q_tensor *norm_bias, float epsilon,
+                                          const b200q_norm_fusion *fusion, const b200q_epilogue *epilogue,
+                                          const b200q_row_scaled *quantized_output, char *error, size_t error_capacity);
 /* The layer's quantized weight view (borrowed; valid while the layer lives). */
 int b200q_linear_layer_weight(b200q_linear_layer *, b200q_row_scaled *weight, char *error, size_t error_capacity);
 

@@ -12,11 +12,18 @@
 //   launch_quantized_gated   src/ops/kernels/quant/quant_gated.h:6-8
 //   quant_linear_candidates / select_linear / path_name
 //                            src/ops/cuda/quantization_policy.h:27-33
+//   ops::pointwise / pointwise_quantize / layer_norm_quantize
+//                            src/ops/sequence.h:35-41,60-63
+//   ops::normalized_quantized_linear
+//                            src/ops/kernels/sequence/norm_projection.h:16-21
 #include "ops/kernels/quant/row_quantize.h"
 #include "ops/kernels/quant/quant_dispatch.h"
 #include "ops/kernels/quant/quant_norm.h"
 #include "ops/kernels/quant/quant_gated.h"
 #include "ops/cuda/quantization_policy.h"
+#include "ops/sequence.h"
+#include "ops/kernels/sequence/norm_projection.h"
+#include "runtime/cuda_context.h"
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cstdio>
@@ -65,8 +72,130 @@ __global__ void residual_add_f32(__nv_bfloat16 *y, const float *residual, size_t
 }
 } // namespace
 
+// The reference's sequence operators take their stream from the engine's thread-bound context
+// (src/ops/cuda/execution_context.h). The engine's context class is built by parts of the reference
+// that are not compiled here, so this shim answers `execution_context` itself with a stand-in of the
+// same type whose only live fields are the device ordinal and the stream; nothing else is read by
+// the operators bound below.
+namespace {
+thread_local cudaStream_t g_stream = nullptr;
+}
+namespace tts {
+CudaContext &execution_context(int device) {
+    alignas(CudaContext) static thread_local unsigned char storage[sizeof(CudaContext)];
+    auto *context = reinterpret_cast<CudaContext *>(storage);
+    *const_cast<int *>(&context->device) = device;
+    *const_cast<cudaStream_t *>(&context->stream) = g_stream;
+    return *context;
+}
+} // namespace tts
+
+// POD mirrors of ops::Epilogue / ops::NormFusion for the tests (all pointers device pointers or null).
+struct ttsref_view {
+    void *data;
+    int rows, cols, stride;
+};
+struct ttsref_epilogue {
+    ttsref_view bias, residual, raw, gate, condition;
+    float value_scale, output_scale, residual_scale, alpha;
+    int activation, rows_per_sequence, valid_rows_per_sequence, input_repeat;
+    const int *residual_rows;
+};
+struct ttsref_fusion {
+    ttsref_view residual, projection_bias, raw, gate, shift, scale;
+    int rows_per_sequence;
+    const int *source_rows;
+};
+namespace {
+tts::TensorView view_of(const ttsref_view &v, int type) {
+    if (!v.data) return {};
+    return tts::TensorView(v.data, v.rows, v.cols, type_of(type), v.stride, 0);
+}
+tts::ops::Epilogue epilogue_of(const ttsref_epilogue *e, int type) {
+    tts::ops::Epilogue out;
+    if (!e) return out;
+    out.bias = view_of(e->bias, type);
+    out.residual = view_of(e->residual, type);
+    out.raw = view_of(e->raw, type);
+    out.gate = view_of(e->gate, type);
+    out.condition = view_of(e->condition, type);
+    out.value_scale = e->value_scale;
+    out.output_scale = e->output_scale;
+    out.residual_scale = e->residual_scale;
+    out.alpha = e->alpha;
+    out.activation = static_cast<tts::ops::Activation>(e->activation);
+    out.rows_per_sequence = e->rows_per_sequence;
+    out.valid_rows_per_sequence = e->valid_rows_per_sequence;
+    out.input_repeat = e->input_repeat;
+    out.residual_rows = e->residual_rows;
+    return out;
+}
+tts::ops::NormFusion fusion_of(const ttsref_fusion *f, int type) {
+    tts::ops::NormFusion out;
+    if (!f) return out;
+    out.residual = view_of(f->residual, type);
+    out.projection_bias = view_of(f->projection_bias, type);
+    out.raw = view_of(f->raw, type);
+    out.gate = view_of(f->gate, type);
+    out.shift = view_of(f->shift, type);
+    out.scale = view_of(f->scale, type);
+    out.rows_per_sequence = f->rows_per_sequence;
+    out.source_rows = f->source_rows;
+    return out;
+}
+} // namespace
+
 extern "C" {
 const char *ttsref_last_error() { return g_error.c_str(); }
+
+int ttsref_pointwise(const ttsref_view *x, const ttsref_view *y, int type, const ttsref_epilogue *epilogue, void *stream) {
+    return guarded([&] {
+        g_stream = static_cast<cudaStream_t>(stream);
+        tts::ops::pointwise(view_of(*x, type), view_of(*y, type), epilogue_of(epilogue, type));
+    });
+}
+
+int ttsref_pointwise_quantize(const ttsref_view *x, int type, void *values, float *scales, int rows, int cols, int format,
+                              int group, int rotation, const ttsref_epilogue *epilogue, const ttsref_view *retained,
+                              int multiprocessors, void *stream) {
+    return guarded([&] {
+        g_stream = static_cast<cudaStream_t>(stream);
+        tts::ops::pointwise_quantize(view_of(*x, type), scaled_view(values, scales, rows, cols, format, group, rotation),
+                                     epilogue_of(epilogue, type), retained ? view_of(*retained, type) : tts::TensorView{},
+                                     multiprocessors);
+    });
+}
+
+int ttsref_layer_norm_quantize(const ttsref_view *x, int type, void *values, float *scales, int rows, int cols, int format,
+                               int group, int rotation, const ttsref_view *weight, const ttsref_view *bias, float epsilon,
+                               const ttsref_fusion *fusion, const ttsref_view *retained, void *stream) {
+    return guarded([&] {
+        g_stream = static_cast<cudaStream_t>(stream);
+        tts::ops::layer_norm_quantize(view_of(*x, type), scaled_view(values, scales, rows, cols, format, group, rotation),
+                                      weight ? view_of(*weight, type) : tts::TensorView{},
+                                      bias ? view_of(*bias, type) : tts::TensorView{}, epsilon, fusion_of(fusion, type),
+                                      retained ? view_of(*retained, type) : tts::TensorView{});
+    });
+}
+
+// Returns 1 when the reference's fused kernel ran, 0 when it declined, -1 on error.
+int ttsref_normalized_quantized_linear(const ttsref_view *x, int type, const ttsref_view *normalized,
+                                       const ttsref_view *norm_weight, const ttsref_view *norm_bias, float epsilon,
+                                       const ttsref_fusion *fusion, void *weight_values, float *weight_scales, int channels,
+                                       int cols, int format, const ttsref_view *output, const ttsref_epilogue *epilogue,
+                                       void *encoded_values, float *encoded_scales, void *stream) {
+    bool taken = false;
+    int rc = guarded([&] {
+        tts::RowScaledView encoded;
+        if (encoded_values) encoded = scaled_view(encoded_values, encoded_scales, x->rows, cols, format, 0, 0);
+        taken = tts::ops::normalized_quantized_linear(
+            static_cast<cudaStream_t>(stream), view_of(*x, type), normalized ? view_of(*normalized, type) : tts::TensorView{},
+            norm_weight ? view_of(*norm_weight, type) : tts::TensorView{}, norm_bias ? view_of(*norm_bias, type) : tts::TensorView{},
+            epsilon, fusion_of(fusion, type), scaled_view(weight_values, weight_scales, channels, cols, format, 0, 0),
+            view_of(*output, type), epilogue_of(epilogue, type), 1 << 30, encoded, nullptr);
+    });
+    return rc ? rc : (taken ? 1 : 0);
+}
 
 int ttsref_row_quantize(void *source, int rows, int cols, int stride, int source_type, void *values,
                         float *scales, int format, int group, int rotation, void *stream) {

@@ -136,6 +136,46 @@ def load() -> Oracle:
     return Oracle(C.CDLL(str(ORACLE_SO)))
 
 
+class RefView(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("rows", C.c_int), ("cols", C.c_int), ("stride", C.c_int)]
+
+
+class RefEpilogue(C.Structure):
+    _fields_ = [("bias", RefView), ("residual", RefView), ("raw", RefView), ("gate", RefView), ("condition", RefView),
+                ("value_scale", C.c_float), ("output_scale", C.c_float), ("residual_scale", C.c_float), ("alpha", C.c_float),
+                ("activation", C.c_int), ("rows_per_sequence", C.c_int), ("valid_rows_per_sequence", C.c_int),
+                ("input_repeat", C.c_int), ("residual_rows", C.c_void_p)]
+
+
+class RefFusion(C.Structure):
+    _fields_ = [("residual", RefView), ("projection_bias", RefView), ("raw", RefView), ("gate", RefView), ("shift", RefView),
+                ("scale", RefView), ("rows_per_sequence", C.c_int), ("source_rows", C.c_void_p)]
+
+
+def ref_view(t) -> RefView:
+    """torch CUDA tensor (1-D or 2-D, dense inner axis) or None -> the shim's view struct."""
+    if t is None:
+        return RefView(None, 0, 0, 0)
+    if t.dim() == 1:
+        t = t.unsqueeze(0)
+    stride = t.stride(0) if t.shape[0] > 1 and t.stride(0) != t.shape[1] else 0
+    return RefView(t.data_ptr(), t.shape[0], t.shape[1], stride)
+
+
+def ref_epilogue(bias=None, residual=None, raw=None, gate=None, condition=None, value_scale=1.0, output_scale=1.0,
+                 residual_scale=1.0, alpha=0.1, activation=0, rows_per_sequence=1, valid_rows_per_sequence=0, input_repeat=1,
+                 residual_rows=None) -> RefEpilogue:
+    return RefEpilogue(ref_view(bias), ref_view(residual), ref_view(raw), ref_view(gate), ref_view(condition), value_scale,
+                       output_scale, residual_scale, alpha, activation, rows_per_sequence, valid_rows_per_sequence,
+                       input_repeat, residual_rows.data_ptr() if residual_rows is not None else None)
+
+
+def ref_fusion(residual=None, projection_bias=None, raw=None, gate=None, shift=None, scale=None, rows_per_sequence=1,
+               source_rows=None) -> RefFusion:
+    return RefFusion(ref_view(residual), ref_view(projection_bias), ref_view(raw), ref_view(gate), ref_view(shift),
+                     ref_view(scale), rows_per_sequence, source_rows.data_ptr() if source_rows is not None else None)
+
+
 def load_reference():
     if not REF_SO.exists():
         return None
@@ -148,6 +188,13 @@ def load_reference():
                                                                              C.c_int, C.c_float, C.c_int, C.c_void_p]
     lib.ttsref_quantized_gated.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p] + [C.c_int] * 6 + [C.c_void_p]
     lib.ttsref_residual_add_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    view, ep, fu = C.POINTER(RefView), C.POINTER(RefEpilogue), C.POINTER(RefFusion)
+    lib.ttsref_pointwise.argtypes = [view, view, C.c_int, ep, C.c_void_p]
+    lib.ttsref_pointwise_quantize.argtypes = [view, C.c_int, C.c_void_p, C.c_void_p] + [C.c_int] * 5 + [ep, view, C.c_int, C.c_void_p]
+    lib.ttsref_layer_norm_quantize.argtypes = [view, C.c_int, C.c_void_p, C.c_void_p] + [C.c_int] * 5 + [view, view, C.c_float, fu,
+                                                                                                    view, C.c_void_p]
+    lib.ttsref_normalized_quantized_linear.argtypes = [view, C.c_int, view, view, view, C.c_float, fu, C.c_void_p, C.c_void_p,
+                                                       C.c_int, C.c_int, C.c_int, view, ep, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.ttsref_candidates.argtypes = [C.c_int] * 6 + [C.c_size_t, C.c_size_t, C.c_void_p, C.c_int]
     lib.ttsref_select.argtypes = [C.c_int] * 7 + [C.c_size_t, C.c_void_p, C.c_char_p, C.c_int]
     return lib

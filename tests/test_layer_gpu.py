@@ -72,3 +72,71 @@ def test_layer_requantizes_output_for_next_layer(oracle, ctx_factory):
     want_q, want_s = oracle.row_quantize(bits(out), I8)
     assert np.array_equal(nxt.values.cpu().numpy(), want_q) and np.array_equal(nxt.scales.cpu().numpy().ravel(), want_s)
     layer.close()
+
+
+def test_phase_switch_plan_prepare_execute(ctx_factory, oracle):
+    """reference: Linear::apply_context (src/layers/linear.cpp:64-76): Plan and Capture launch nothing, Prepare
+    plans and sizes the scratch, Execute runs; Execute beyond the prepared rows fails instead of allocating."""
+    from breeze_tts_cpp_b200 import B200QError, ops
+    ctx = ops.Context("int8", device=0)  # a fresh context: its plans are not sealed yet
+    k, n = 512, 384
+    _, w = dev16(oracle, synth.weights(n, k, 5))
+    b16, bias = dev16(oracle, synth.weights(1, n, 6, std=0.3))
+    layer = ops.Linear(ctx, [w], bias=bias, max_rows=1)
+    x16, x = dev16(oracle, synth.activations(24, k, seed=8))
+    out = torch.full((24, n), 7.0, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(B200QError):
+        layer.apply(ops.Linear.EXECUTE, 24, x, out)       # never prepared for 24 rows
+    for mode in (ops.Linear.PLAN, ops.Linear.CAPTURE):
+        layer.apply(mode, 24, x, out)
+        assert float(out.float().min()) == 7.0            # nothing ran
+    layer.apply(ops.Linear.PREPARE, 24, x, out, activation=1)
+    assert float(out.float().min()) == 7.0
+    ctx.seal()
+    layer.apply(ops.Linear.EXECUTE, 24, x, out, activation=1)
+    wq, sw = oracle.row_quantize(bits(w), I8)
+    xq, sx = oracle.row_quantize(x16, I8)
+    want, _ = oracle.quant_linear(xq, sx, wq, sw, I8, bias=b16.ravel(), activation=1)
+    assert ctx.status() == 0 and np.array_equal(bits(out), want)
+    # segments: scatter two row ranges of the input to other rows of the output
+    scattered = torch.zeros(24, n, dtype=torch.bfloat16, device="cuda")
+    layer.forward_segments(ops.Linear.EXECUTE, 24, x, [(0, 8, 16), (8, 16, 0)], scattered)
+    plain = torch.empty(24, n, dtype=torch.bfloat16, device="cuda")
+    layer.forward_segments(ops.Linear.EXECUTE, 24, x, [], plain)
+    assert torch.equal(scattered[16:24], plain[0:8]) and torch.equal(scattered[0:16], plain[8:24])
+    layer.close()
+    ctx.close()
+
+
+@pytest.mark.parametrize("k,fused", [(512, True), (1024, False)])
+def test_normalized_forward_fused_and_two_step_agree(ctx_factory, oracle, k, fused):
+    """reference: Linear::normalized_forward (src/layers/linear.cpp:195-214). For K <= 512 one launch does
+    LayerNorm + quantize + projection; beyond that LayerNorm + quantize is followed by the GEMM. Both give
+    the result of running the two steps by hand."""
+    from breeze_tts_cpp_b200 import ops
+    ctx = ctx_factory("int8")
+    n, rows = 256, 12
+    _, w = dev16(oracle, synth.weights(n, k, 5))
+    _, bias = dev16(oracle, synth.weights(1, n, 6, std=0.3))
+    layer = ops.Linear(ctx, [w], bias=bias, max_rows=rows)
+    _, x = dev16(oracle, synth.activations(rows, k, seed=8))
+    _, gamma = dev16(oracle, 1.0 + synth.weights(1, k, 7, std=0.2))
+    _, beta = dev16(oracle, synth.weights(1, k, 8, std=0.2))
+    out = torch.empty(rows, n, dtype=torch.bfloat16, device="cuda")
+    normalized = torch.zeros(rows, k, dtype=torch.bfloat16, device="cuda")
+    layer.normalized_forward(x, out, gamma, beta, 1e-5, normalized=normalized, activation=1)
+    assert ctx.status() == 0
+    by_hand_q = ctx.layer_norm_quantize(x, ops.RowScaledView.empty(rows, k, I8), gamma, beta, 1e-5)
+    weight = layer.weight()
+    wv = ops.RowScaledView(torch.empty(0), torch.empty(0), I8)
+    wv.c = lambda: weight  # the layer's own quantized weight view
+    ctx.prepare_quantized(rows, n, k)
+    by_hand = torch.empty_like(out)
+    ctx.matmul(by_hand_q, wv, by_hand, bias=bias, activation=1)
+    if fused:  # the fused kernel multiplies (acc * sw) * sx, the GEMM (acc * sx) * sw: at most one bf16 step apart
+        a, b = out.double(), by_hand.double()
+        assert float(((a - b).abs() / torch.maximum(a.abs(), b.abs()).clamp_min(1e-6)).max()) <= 2.0 ** -7
+    else:
+        assert torch.equal(out.view(torch.int16), by_hand.view(torch.int16))
+    assert float(normalized.float().abs().max()) > 0
+    layer.close()
