@@ -77,6 +77,7 @@ SIGNATURES = {
     "b200q_linear_layer_weight": (C.c_int, (C.c_void_p, _PR, *_ERR)),
     "b200q_quant_linear_static": (C.c_int, (C.c_int32, C.c_void_p, _PP, _PR, _PR, _PT, _PE, *_ERR)),
     "b200q_static_status": (C.c_int, (C.c_int32, C.c_void_p, C.POINTER(C.c_int32), *_ERR)),
+    "b200q_inject_wait_expiry": (C.c_int, (C.c_int32, C.c_int64, *_ERR)),
     "b200q_status": (C.c_int, (C.c_void_p, C.POINTER(C.c_int32), *_ERR)),
     "b200q_multiprocessors": (C.c_int, (C.c_void_p,)),
     "b200q_row_capacity": (C.c_int32, (C.c_int32, C.c_uint32)),

@@ -304,6 +304,9 @@ int b200q_linear_layer_weight(b200q_linear_layer *l, b200q_row_scaled *weight, c
         *weight = {put(w.values), put(w.scales), w.group_size, w.rotation_size};
     });
 }
+int b200q_inject_wait_expiry(int32_t extra_bytes, int64_t limit_cycles, char *error, size_t capacity) {
+    return guarded(error, capacity, [&] { quant_linear_inject_wait_expiry(extra_bytes, limit_cycles); });
+}
 int b200q_status(b200q_context *c, int32_t *status, char *error, size_t capacity) {
     return guarded(error, capacity, [&] {
         auto &gpu = context_of(c);

@@ -41,6 +41,11 @@ size_t quant_linear_workspace_bytes(LinearPath, KernelProblem);
 void quant_linear_initialize(int device);
 // Zeroes the ticket/status header of a fresh workspace (asynchronously on `stream`).
 void quant_linear_reset_workspace(void *workspace, size_t workspace_bytes, cudaStream_t stream);
+// Failure-path exercise without a GPU fault: the NEXT weight-streaming GEMM launched from this thread
+// arms its first weight barrier for `extra_bytes` more than its (fully completing) copy delivers and
+// lets every device-side wait give up after `limit_cycles` SM cycles, so the kernel runs to its normal
+// teardown, stores nothing and raises the status word. One-shot; nothing is left in flight.
+void quant_linear_inject_wait_expiry(int extra_bytes, long long limit_cycles);
 // Blocking read of the status word: 0 = clean, otherwise 1 + index of the tile whose bounded wait gave up.
 int quant_linear_status(const void *workspace, cudaStream_t stream);
 } // namespace tts

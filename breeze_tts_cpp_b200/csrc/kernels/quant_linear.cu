@@ -240,6 +240,18 @@ int quant_linear_status(const void *workspace, cudaStream_t stream) {
 // Split-K partials live in shared memory, so every path needs only the status header.
 size_t quant_linear_workspace_bytes(LinearPath, KernelProblem) { return kWorkspaceHeader; }
 
+namespace {
+struct WaitExpiry {
+    int extra_bytes = 0;
+    long long limit_cycles = 0;
+};
+thread_local WaitExpiry pending_expiry;
+} // namespace
+void quant_linear_inject_wait_expiry(int extra_bytes, long long limit_cycles) {
+    if (extra_bytes < 0 || extra_bytes > 1024 || limit_cycles < 0) throw std::invalid_argument("invalid wait-expiry injection");
+    pending_expiry = {extra_bytes, limit_cycles};
+}
+
 LinearPath select_tcgen05_path(KernelProblem p, Type format, int sms, size_t workspace_bytes) {
     return select_linear(p, KernelLimits{false, 0, workspace_bytes}, format, ChipModel::b200(sms));
 }
@@ -268,8 +280,9 @@ void launch_quant_linear(LinearPath config, KernelProblem shape, const void *inp
         throw std::invalid_argument("quantized GEMM unsupported shape");
     if (format == Type::I8 && shape.reduction > INT32_MAX / (128 * 128))
         throw std::invalid_argument("INT8 reduction can overflow INT32");
-    if ((shape.input_group && shape.input_group != kBlockK) || (shape.weight_group && shape.weight_group != kBlockK))
-        throw std::invalid_argument("the tcgen05 GEMM supports K groups of 128 only");
+    for (int group : {shape.input_group, shape.weight_group})
+        if (group && group != 32 && group != 64 && group != 128)
+            throw std::invalid_argument("unsupported GEMM quantization group size");
     if (!input || !xs || !weights || !ws || !y) throw std::invalid_argument("quantized GEMM null operand");
     const int kb_total = (shape.reduction + kBlockK - 1) / kBlockK;
     const int bn = config.tokens, splits = config.splits;
@@ -344,13 +357,17 @@ void launch_quant_linear(LinearPath config, KernelProblem shape, const void *inp
         return;
     }
     const CUtensorMap map_x = operand_map(input, shape.rows, shape.reduction, bn, false);
-    LaunchShape launch = launch_shape(bn, grouped, (kb_total + splits - 1) / splits, splits);
+    LaunchShape launch = launch_shape(bn, grouped, (kb_total + splits - 1) / splits, splits,
+                                      group_units(shape.input_group, shape.weight_group));
     if (!launch.fits)
         throw std::invalid_argument("quantized GEMM: this tile/split combination exceeds shared memory; use more splits");
     // A K-group CTA allocates all 512 columns of tensor memory, so two of them must never share a
     // multiprocessor (the second allocation would wait for the first CTA, and with split-K clusters
     // two such waits can form a cycle): ask for more than half of the shared memory.
     if (grouped) launch.smem = std::max(launch.smem, size_t(120) * 1024);
+    args.expiry_extra_bytes = pending_expiry.extra_bytes; // one-shot, only the weight-streaming kernel honours it
+    args.wait_limit_cycles = pending_expiry.limit_cycles;
+    pending_expiry = {};
     args.stages = launch.stages;
     args.tile_region = int(launch.tile_region);
     args.owned_passes = launch.owned_passes;

@@ -19,16 +19,22 @@ struct LaunchShape {
     int stages = 0, owned_passes = 0;
     size_t tile_region = 0, smem = 0;
 };
+// K groups per 128-byte K block (1, 2 or 4 for group widths 128, 64, 32): the narrower of the two
+// operands' widths decides, an operand without K groups counts as 128.
+inline int group_units(int input_group, int weight_group) {
+    const int narrow = std::min(input_group ? input_group : kBlockK, weight_group ? weight_group : kBlockK);
+    return kBlockK / std::max(32, narrow);
+}
 // Shared memory of one CTA of the weight-streaming kernel: alignment slack + pipeline stages
 // (unsplit: later the transposed [token][channel] tile of 4-byte partials) + split-K slots the
-// cluster peers push into + K-group scales of the CTA's K range.
-inline LaunchShape launch_shape(int bn, bool grouped, int kb_per_split, int splits) {
+// cluster peers push into + the K-group scales of the CTA's K range, one pair per group.
+inline LaunchShape launch_shape(int bn, bool grouped, int kb_per_split, int splits, int units = 1) {
     const size_t stage = size_t(kBlockChannels + bn) * kBlockK;
     const size_t transposed = splits == 1 ? size_t(bn) * kBlockChannels * sizeof(float) : 0;
     const int passes = (bn + kRowsPerPass - 1) / kRowsPerPass;
     const int owned = splits > 1 ? (passes + splits - 1) / splits : 0;
     const size_t reduce = size_t(splits > 1 ? splits : 0) * owned * kRowsPerPass * kBlockChannels * sizeof(float);
-    const size_t scales = grouped ? size_t(kb_per_split) * (bn + kBlockChannels) * sizeof(float) : 0;
+    const size_t scales = grouped ? size_t(kb_per_split) * units * (bn + kBlockChannels) * sizeof(float) : 0;
     const size_t fixed = 1024 + reduce + scales;
     LaunchShape shape;
     if (fixed + std::max(2 * stage, transposed) > kSmemBudget) return shape;

@@ -9,10 +9,12 @@
 //
 //   per-row scales : out[m,n] = D((float(acc) * sx[m]) * sw[n])
 //                    (reference order: src/ops/kernels/quant/quant_gemm_sm80.cu:22-29)
-//   K128 groups    : r += float(p_g) * (sx[g,m] * sw[g,n]) for g ascending, out = D(r)
-//                    (reference: src/ops/kernels/quant/quant_grouped.cu:85-168); every K block
-//                    accumulates into a fresh tensor-memory buffer that the epilogue warps drain
-//                    and rescale while the next block's MMAs run.
+//   K groups       : r += float(p_g) * (sx[g,m] * sw[g,n]) for g ascending, out = D(r)
+//                    (reference: src/ops/kernels/quant/quant_grouped.cu:85-168); every group of
+//                    128, 64 or 32 along K (the narrower of the two operands' group widths, as in
+//                    the reference, :185-199) accumulates into a fresh tensor-memory buffer that the
+//                    epilogue warps drain and rescale while the next group's MMAs run. A 128-byte K
+//                    block is four 32-byte MMAs, so it splits into one, two or four such units.
 //   split-K        : the splits of one output tile form a thread-block cluster. Token rows are dealt
 //                    to the CTAs in blocks of 16; every CTA pushes its partial rows straight from
 //                    tensor memory into the owner's shared memory (one slot per split, remote
@@ -64,6 +66,11 @@ struct GemmArgs {
     int owned_passes; // split-K: 16-row passes each CTA of the cluster may own (slots per split)
     int vector_io;   // every global row touched by the epilogue is 16-byte aligned
     int *status;
+    // Failure-path exercise (host-side injection, see quant_linear_inject_wait_expiry): the first weight
+    // barrier expects `expiry_extra_bytes` more than its copy delivers, and every wait gives up after
+    // `wait_limit_cycles` (0 = the regular limit). Both zero in normal operation.
+    int expiry_extra_bytes;
+    long long wait_limit_cycles;
     FusedEpilogue ep;
 };
 
@@ -155,6 +162,9 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const int kb_begin = int(int64_t(kb_total) * split / splits);
     const int kb_end = int(int64_t(kb_total) * (split + 1) / splits);
     const int kb_count = kb_end - kb_begin;
+    // K-group mode: accumulation units per 128-byte K block (1, 2 or 4) and MMAs per unit.
+    const int unit_k = Grouped ? min(a.input_group ? a.input_group : kBlockK, a.weight_group ? a.weight_group : kBlockK) : kBlockK;
+    const int units = kBlockK / unit_k, unit_mmas = 4 / units;
     const int tile_linear = blockIdx.y * gridDim.x + blockIdx.x;
     const int valid_tokens = min(BN, a.m - m0);
 
@@ -179,6 +189,7 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     ptx::tcgen05_fence_after();
     const uint32_t tmem_base = tmem_slot;
     volatile int *abort_ptr = &abort_flag;
+    const long long wait_limit = a.wait_limit_cycles > 0 ? a.wait_limit_cycles : ptx::kWaitLimitCycles;
     // The next kernel in the stream may begin its own prologue; peers learn that this CTA is running.
     ptx::launch_dependents();
     if (splits > 1) ptx::cluster_arrive();
@@ -195,7 +206,7 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             const int ahead = min(a.stages, kb_count);
             for (int i = 0; i < ahead; ++i) {
                 const uint32_t bar = ptx::smem_u32(&full_bar[i]);
-                ptx::mbar_arrive_expect_tx(bar, kWeightBytes);
+                ptx::mbar_arrive_expect_tx(bar, kWeightBytes + (i == 0 ? uint32_t(a.expiry_extra_bytes) : 0u));
                 ptx::tma_load_2d(tiles_base + uint32_t(i) * kStageBytes, &map_w, bar, (kb_begin + i) * kBlockK, n0);
             }
             ptx::wait_for_upstream();
@@ -206,7 +217,7 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             int stage = ahead == a.stages ? 0 : ahead;
             uint32_t phase = ahead == a.stages ? 1u : 0u;
             for (int kb = kb_begin + ahead; kb < kb_end; ++kb) {
-                if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_ptr)) break;
+                if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_ptr, wait_limit)) break;
                 const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
                 const uint32_t dst = tiles_base + uint32_t(stage) * kStageBytes;
                 ptx::mbar_arrive_expect_tx(bar, kStageBytes);
@@ -225,27 +236,44 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             // collect those barriers now, off the critical path, then wait once for the activations.
             const int ahead = min(a.stages, kb_count);
             bool ok = true;
-            for (int i = 0; i < ahead && ok; ++i) ok = ptx::mbar_wait(ptx::smem_u32(&full_bar[i]), 0u, abort_ptr);
-            ok = ok && ptx::mbar_wait(ptx::smem_u32(&x_full), 0u, abort_ptr);
+            for (int i = 0; i < ahead && ok; ++i) ok = ptx::mbar_wait(ptx::smem_u32(&full_bar[i]), 0u, abort_ptr, wait_limit);
+            ok = ok && ptx::mbar_wait(ptx::smem_u32(&x_full), 0u, abort_ptr, wait_limit);
             ok = __all_sync(0xffffffffu, ok);
             // The prefetched stages need no barrier at all any more, so their MMAs go out back to back
             // (any shared-memory access between MMA issues stalls the issuing warp for a couple of
             // hundred cycles). Stage i holds K block i here; in K-group mode K block i also has
             // accumulator i to itself while fresh accumulators last.
+            // Narrow K groups: the MMAs of one 128-byte K block go to `units` accumulators, `unit_mmas`
+            // each; every accumulator reports on its own barrier.
+            auto issue_units = [&](uint32_t lo_w, uint32_t lo_x, uint32_t d_first, int buffer_first) {
+                for (int u = 0; u < units; ++u) {
+                    for (int s = 0; s < unit_mmas; ++s) {
+                        const uint32_t step = uint32_t(2 * (u * unit_mmas + s)); // 32 bytes of K = 2 descriptor units
+                        if (kInt) ptx::mma_i8_lo(d_first + uint32_t(u * BN), lo_w + step, lo_x + step, kIdesc, uint32_t(s > 0));
+                        else ptx::mma_f8_lo(d_first + uint32_t(u * BN), lo_w + step, lo_x + step, kIdesc, uint32_t(s > 0));
+                    }
+                    ptx::tcgen05_commit(ptx::smem_u32(&acc_full[buffer_first + u]));
+                }
+            };
             int first = 0;
             if (ok) {
-                const int burst = Grouped ? min(ahead, kAccBuffers) : ahead;
+                const int burst = Grouped ? min(ahead, kAccBuffers / units) : ahead;
                 ptx::tcgen05_fence_after();
                 for (int it = 0; it < burst; ++it) {
                     const uint32_t tile = tiles_base + uint32_t(it) * kStageBytes;
-                    const uint32_t d = tmem_base + (Grouped ? uint32_t(it * BN) : 0u);
+                    const uint32_t lo_w = ptx::smem_desc_lo_k128(tile), lo_x = ptx::smem_desc_lo_k128(tile + kWeightBytes);
+                    const uint32_t d = tmem_base + (Grouped ? uint32_t(it * units * BN) : 0u);
                     if (ptx::elect_one()) {
-                        const uint32_t accumulate = Grouped ? 0u : uint32_t(it > 0);
-                        if (kInt) ptx::mma_i8_k128(d, ptx::smem_desc_lo_k128(tile), ptx::smem_desc_lo_k128(tile + kWeightBytes), kIdesc, accumulate);
-                        else ptx::mma_f8_k128(d, ptx::smem_desc_lo_k128(tile), ptx::smem_desc_lo_k128(tile + kWeightBytes), kIdesc, accumulate);
+                        if (!Grouped || units == 1) {
+                            const uint32_t accumulate = Grouped ? 0u : uint32_t(it > 0);
+                            if (kInt) ptx::mma_i8_k128(d, lo_w, lo_x, kIdesc, accumulate);
+                            else ptx::mma_f8_k128(d, lo_w, lo_x, kIdesc, accumulate);
+                        } else {
+                            issue_units(lo_w, lo_x, d, it * units);
+                        }
                         // Only a stage that will be refilled needs to report that its MMAs retired.
                         if (it + a.stages < kb_count) ptx::tcgen05_commit(ptx::smem_u32(&empty_bar[it]));
-                        if (Grouped) ptx::tcgen05_commit(ptx::smem_u32(&acc_full[it]));
+                        if (Grouped && units == 1) ptx::tcgen05_commit(ptx::smem_u32(&acc_full[it]));
                     }
                     __syncwarp();
                 }
@@ -255,10 +283,12 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             uint32_t phase = first == a.stages ? 1u : 0u;
             // Refilled stages arrive at the rate memory delivers them, one barrier each.
             for (int it = first; it < kb_count && ok; ++it) {
-                const int buffer = Grouped ? it % kAccBuffers : 0;
-                if (Grouped && it >= kAccBuffers) // the epilogue drained this accumulator's previous K block
-                    ok = ptx::mbar_wait(ptx::smem_u32(&acc_empty[buffer]), (uint32_t(it / kAccBuffers) & 1u) ^ 1u, abort_ptr);
-                if (it >= ahead) ok = ok && ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_ptr);
+                const int buffer = Grouped ? (it * units) % kAccBuffers : 0;
+                if (Grouped && it * units >= kAccBuffers) // the epilogue drained these accumulators' previous groups
+                    for (int u = 0; u < units && ok; ++u)
+                        ok = ptx::mbar_wait(ptx::smem_u32(&acc_empty[buffer + u]),
+                                            (uint32_t((it * units + u) / kAccBuffers) & 1u) ^ 1u, abort_ptr, wait_limit);
+                if (it >= ahead) ok = ok && ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_ptr, wait_limit);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 ptx::tcgen05_fence_after();
@@ -266,11 +296,15 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 const uint32_t lo_w = ptx::smem_desc_lo_k128(tile), lo_x = ptx::smem_desc_lo_k128(tile + kWeightBytes);
                 const uint32_t d = tmem_base + uint32_t(buffer * BN);
                 if (ptx::elect_one()) {
-                    const uint32_t accumulate = Grouped ? 0u : uint32_t(it > 0);
-                    if (kInt) ptx::mma_i8_k128(d, lo_w, lo_x, kIdesc, accumulate);
-                    else ptx::mma_f8_k128(d, lo_w, lo_x, kIdesc, accumulate);
+                    if (!Grouped || units == 1) {
+                        const uint32_t accumulate = Grouped ? 0u : uint32_t(it > 0);
+                        if (kInt) ptx::mma_i8_k128(d, lo_w, lo_x, kIdesc, accumulate);
+                        else ptx::mma_f8_k128(d, lo_w, lo_x, kIdesc, accumulate);
+                    } else {
+                        issue_units(lo_w, lo_x, d, buffer);
+                    }
                     if (it + a.stages < kb_count) ptx::tcgen05_commit(ptx::smem_u32(&empty_bar[stage]));
-                    if (Grouped) ptx::tcgen05_commit(ptx::smem_u32(&acc_full[buffer]));
+                    if (Grouped && units == 1) ptx::tcgen05_commit(ptx::smem_u32(&acc_full[buffer]));
                 }
                 __syncwarp();
                 if (++stage == a.stages) { stage = 0; phase ^= 1u; }
@@ -345,7 +379,7 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 
         if constexpr (!Grouped) {
             for (int c = e_thread; c < BN; c += kEpilogueThreads) sx_tile[c] = c < valid_tokens ? a.sx[m0 + c] : 0.f;
-            ok = ptx::mbar_wait(ptx::smem_u32(&acc_full[0]), 0, abort_ptr);
+            ok = ptx::mbar_wait(ptx::smem_u32(&acc_full[0]), 0, abort_ptr, wait_limit);
             ptx::tcgen05_fence_after();
             if (splits > 1) ptx::cluster_wait(); // every peer is running: its shared memory may be written
             if (ok) {
@@ -363,25 +397,28 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 }
             }
         } else {
-            // Stage this split's group scales once: sx_g[block][token], sw_g[block][channel].
-            float *sx_smem = scale_smem, *sw_smem = scale_smem + size_t(kb_count) * BN;
-            for (int i = e_thread; i < kb_count * BN; i += kEpilogueThreads) {
-                int block = i / BN, token = i % BN;
-                sx_smem[i] = (a.input_group && token < valid_tokens)
-                                 ? a.sx[size_t(kb_begin + block) * a.m + m0 + token] : 1.f;
+            // Stage this split's group scales once, one entry per accumulation unit: sx_g[unit][token],
+            // sw_g[unit][channel]. Each operand is indexed by its own group width; a unit past the end of K
+            // (its accumulator holds zeros) takes scale 1.
+            const int unit_count = kb_count * units;
+            float *sx_smem = scale_smem, *sw_smem = scale_smem + size_t(unit_count) * BN;
+            for (int i = e_thread; i < unit_count * BN; i += kEpilogueThreads) {
+                const int unit = i / BN, token = i % BN, k0 = kb_begin * kBlockK + unit * unit_k;
+                sx_smem[i] = (a.input_group && token < valid_tokens && k0 < a.k)
+                                 ? a.sx[size_t(k0 / a.input_group) * a.m + m0 + token] : 1.f;
             }
-            for (int i = e_thread; i < kb_count * kBlockChannels; i += kEpilogueThreads) {
-                int block = i / kBlockChannels, channel = n0 + i % kBlockChannels;
-                sw_smem[i] = (a.weight_group && channel < a.n) ? a.sw[size_t(kb_begin + block) * a.n + channel] : 1.f;
+            for (int i = e_thread; i < unit_count * kBlockChannels; i += kEpilogueThreads) {
+                const int unit = i / kBlockChannels, channel = n0 + i % kBlockChannels, k0 = kb_begin * kBlockK + unit * unit_k;
+                sw_smem[i] = (a.weight_group && channel < a.n && k0 < a.k) ? a.sw[size_t(k0 / a.weight_group) * a.n + channel] : 1.f;
             }
             asm volatile("bar.sync 1, 256;" ::: "memory");
             float result[kMyChunks * 16];
 #pragma unroll
             for (int c = 0; c < kMyChunks * 16; ++c) result[c] = 0.f;
 #pragma unroll 1
-            for (int it = 0; it < kb_count && ok; ++it) {
+            for (int it = 0; it < unit_count && ok; ++it) {
                 const int buffer = it % kAccBuffers;
-                ok = ptx::mbar_wait(ptx::smem_u32(&acc_full[buffer]), uint32_t(it / kAccBuffers) & 1u, abort_ptr);
+                ok = ptx::mbar_wait(ptx::smem_u32(&acc_full[buffer]), uint32_t(it / kAccBuffers) & 1u, abort_ptr, wait_limit);
                 if (!ok) break;
                 ptx::tcgen05_fence_after();
                 const float scale_w = sw_smem[it * kBlockChannels + channel_in_tile];

@@ -45,14 +45,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // error status instead of hanging the GPU. The limit is counted on the SM's own cycle counter
 // (about two seconds at 2 GHz); the global nanosecond timer is far too slow to read in a hot loop.
 constexpr long long kWaitLimitCycles = 4000000000ll;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          long long limit = kWaitLimitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     for (uint32_t spin = 1;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 255u) == 0) {
             if (*abort_flag) return false;
-            if (clock64() - start > kWaitLimitCycles) {
+            if (clock64() - start > limit) {
                 *abort_flag = 1;
                 return false;
             }

@@ -62,7 +62,8 @@ std::vector<LinearPath> quant_linear_candidates(KernelProblem p, KernelLimits li
     if (group && cover == kGroupedTokens) token_tiles.push_back(64); // the split-K kernel's widest K-group tile below 128
     for (int tokens : token_tiles)
         for (int splits = 1; splits <= std::min(kb_total, kMaxSplits); ++splits) {
-            const LaunchShape shape = launch_shape(tokens, group, blocks(kb_total, splits), splits);
+            const LaunchShape shape = launch_shape(tokens, group, blocks(kb_total, splits), splits,
+                                                   group_units(p.input_group, p.weight_group));
             if (!shape.fits || (limits.shared_bytes && shape.smem > limits.shared_bytes)) continue;
             paths.push_back({LinearKind::Tcgen05, tokens, kBlockChannels, splits});
         }
@@ -95,7 +96,8 @@ double linear_cost(KernelProblem p, LinearPath path, Type, const ChipModel &chip
     const double stage_bytes = double(kBlockChannels + path.tokens) * kBlockK;
     const int64_t ctas = int64_t(blocks(p.channels, kBlockChannels)) * blocks(p.rows, path.tokens) * splits;
     // Small tiles leave room for two CTAs per SM; clusters are placed whole.
-    const LaunchShape shape = launch_shape(path.tokens, grouped(p), per_split, splits);
+    const LaunchShape shape = launch_shape(path.tokens, grouped(p), per_split, splits, group_units(p.input_group, p.weight_group));
+    if (!shape.fits) return std::numeric_limits<double>::infinity();
     const int resident = (!grouped(p) && path.tokens <= 64 && shape.fits && shape.smem <= 108 * 1024) ? 2 : 1;
     const int64_t slots = std::max<int64_t>(splits, int64_t(sms) * resident / splits * splits);
     const double waves = double((ctas + slots - 1) / slots);

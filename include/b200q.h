@@ -220,6 +220,13 @@ int b200q_quant_linear_static(int32_t device, void *stream, const b200q_path *pa
  * nothing. Each static call clears the word before it launches, so ask before the next call. */
 int b200q_static_status(int32_t device, void *stream, int32_t *status, char *error, size_t error_capacity);
 
+/* No counterpart in the reference. Exercises the failure path without faulting the GPU: the next
+ * GEMM this thread launches through b200q_quant_linear (weight-streaming kernel, i.e. a token tile
+ * below 256 or a split) expects `extra_bytes` (1..1024) more on its first weight barrier than the
+ * copy delivers and gives up every device-side wait after `limit_cycles` SM cycles; it then leaves
+ * through its normal teardown, writes no output and sets the status word. One-shot. */
+int b200q_inject_wait_expiry(int32_t extra_bytes, int64_t limit_cycles, char *error, size_t error_capacity);
+
 /* Blocks until the context's stream is idle and returns the device status word through `status`:
  * 0 = clean; nonzero = a bounded device-side wait gave up (results are invalid). */
 int b200q_status(b200q_context *, int32_t *status, char *error, size_t error_capacity);

@@ -211,3 +211,67 @@ def test_k_group_matches_reference_kernels(reference_kernels, ctx_factory, oracl
     assert rc == 0, reference_kernels.ttsref_last_error()
     torch.cuda.synchronize()
     assert rel_err(mine.float().cpu().numpy(), theirs.float().cpu().numpy()) < tol
+
+
+def test_bounded_wait_expires_into_the_status_word(oracle):
+    """The failure path, made on the host: one barrier is armed for a byte more than its (fully completing)
+    copy delivers and the wait limit is cut to about a millisecond, so the kernel gives up, leaves through its
+    normal teardown, stores nothing and raises the status word. Nothing faults and nothing stays in flight: the
+    next launch on the same context computes the right answer."""
+    from breeze_tts_cpp_b200 import _lib, ops
+    ctx = ops.Context("int8", device=0)
+    m, n, k = 16, 256, 512
+    (xq, sx, wq, sw), (xv, wv) = make_operands(oracle, m, n, k, I8, 0, 0, seed=5)
+    out = torch.full((m, n), 3.0, dtype=torch.bfloat16, device="cuda")
+    assert ctx.status() == 0
+    _lib.call("b200q_inject_wait_expiry", 1, 2_000_000)
+    ctx.quant_linear((TCGEN05, 16, 128, 1), xv, wv, out)
+    assert ctx.status() != 0
+    assert float(out.float().min()) == 3.0 and float(out.float().max()) == 3.0  # no row was stored
+    ctx.close()
+    ctx = ops.Context("int8", device=0)  # a fresh workspace header; the injection was one-shot
+    ctx.quant_linear((TCGEN05, 16, 128, 1), xv, wv, out)
+    want, _ = oracle.quant_linear(xq, sx, wq, sw, I8)
+    assert ctx.status() == 0 and np.array_equal(bf16_bits(out), want)
+    ctx.close()
+
+
+NARROW_GROUPS = [  # m, n, k, activation group, weight group, token tile, splits
+    (16, 256, 512, 32, 32, 16, 1), (5, 384, 768, 64, 64, 16, 3), (64, 512, 2048, 128, 32, 64, 2), (100, 256, 1024, 64, 128, 128, 1),
+    (16, 2048, 6144, 32, 32, 16, 4), (8, 144, 160, 32, 32, 16, 1), (33, 640, 1536, 64, 32, 64, 4), (16, 256, 1024, 0, 64, 16, 2),
+]
+
+
+@pytest.mark.parametrize("fmt,tol", [(I8, 1e-2), (FP8, 2e-2)])
+@pytest.mark.parametrize("m,n,k,gx,gw,tokens,splits", NARROW_GROUPS)
+def test_k_groups_of_32_and_64(oracle, reference_kernels, ctx_factory, fmt, tol, m, n, k, gx, gw, tokens, splits):
+    """Every RowScaledView group width the reference executes (32, 64, 128; the two operands may differ, the
+    narrower one is the accumulation unit — reference: quant_grouped.cu:185-199), against the oracle and the
+    reference's grouped kernel."""
+    from breeze_tts_cpp_b200 import ops
+    ctx = ctx_factory("group_int8" if fmt == I8 else "group_fp8")
+    x16 = oracle.to_bf16(synth.activations(m, k, m + k, student_t=3.0))
+    w16 = oracle.to_bf16(synth.weights(n, k, m + k + 1))
+    xq, sx = oracle.row_quantize(x16, fmt, gx, 0)
+    wq, sw = oracle.row_quantize(w16, fmt, gw, 0)
+    scales = lambda s, rows, g: torch.from_numpy(s).cuda().reshape(-1, rows) if g else torch.from_numpy(s).cuda().reshape(rows, 1)
+    xv = ops.RowScaledView(torch.from_numpy(xq).cuda(), scales(sx, m, gx), fmt, gx, 0)
+    wv = ops.RowScaledView(torch.from_numpy(wq).cuda(), scales(sw, n, gw), fmt, gw, 0)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    ctx.quant_linear((TCGEN05, tokens, 128, splits), xv, wv, out)
+    _, exact = oracle.quant_linear(xq, sx, wq, sw, fmt, gx, gw)
+    assert ctx.status() == 0
+    assert rel_err(out.float().cpu().numpy(), exact) < tol
+    planned = torch.empty_like(out)
+    ctx.prepare_quantized(m, n, k, groups=(gx, gw))
+    ctx.matmul(xv, wv, planned)
+    assert ctx.status() == 0 and rel_err(planned.float().cpu().numpy(), exact) < tol
+    if gx and k % 128 == 0:  # the reference kernel wants group scales on the activations and whole K128 stages
+        theirs = torch.empty_like(out)
+        workspace = torch.zeros(8 << 20, dtype=torch.uint8, device="cuda")
+        rc = reference_kernels.ttsref_quant_linear(4, 16, 64, 1, m, n, k, gx, gw, xv.values.data_ptr(), xv.scales.data_ptr(),
+                                                   wv.values.data_ptr(), wv.scales.data_ptr(), theirs.data_ptr(),
+                                                   workspace.data_ptr(), workspace.numel(), None, fmt, BF16)
+        assert rc == 0, reference_kernels.ttsref_last_error()
+        torch.cuda.synchronize()
+        assert rel_err(out.float().cpu().numpy(), theirs.float().cpu().numpy()) < tol
