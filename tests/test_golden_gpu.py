@@ -25,10 +25,18 @@ def test_golden_case(ctx_factory, case):
     assert np.array_equal(xv.values.cpu().numpy(), data["xq"]) and np.array_equal(wv.values.cpu().numpy(), data["wq"])
     assert np.array_equal(xv.scales.cpu().numpy().reshape(data["sx"].shape), data["sx"])
     assert np.array_equal(wv.scales.cpu().numpy().reshape(data["sw"].shape), data["sw"])
+    # the reference kernels' own bytes and scales, recorded in the fixture
+    assert np.array_equal(xv.scales.cpu().numpy().reshape(data["ref_sx"].shape), data["ref_sx"])
+    differs = xv.values.cpu().numpy() != data["ref_xq"]
+    if fmt == FP8:
+        differs &= ((xv.values.cpu().numpy() | data["ref_xq"]) & 0x7F) != 0
+    assert not differs.any()
     ctx.prepare_quantized(m, n, k)
     out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
     ctx.matmul(xv, wv, out)
     got = out.view(torch.int16).cpu().numpy().view(np.uint16)
+    if fmt == I8 and not group:
+        assert np.array_equal(got, data["ref_out16"])  # the reference CUTLASS kernel's bits
     want = data["out16"]
     if fmt == I8 and not group:
         assert np.array_equal(got, want)

@@ -1,7 +1,7 @@
 """Pins of the CPU oracle. The reference ships no tests or golden vectors for this path, so the
 pins are hand-derived known answers for every rule the oracle restates (each test names the
 reference lines the rule comes from), algebraic properties, and the committed fixtures in
-tests/golden/."""
+tests/golden/, which also hold the outputs of the reference's own kernels on the same inputs."""
 import json
 from pathlib import Path
 
@@ -205,3 +205,62 @@ def test_producers_keep_reference_rounding_points(oracle):
     act, q, s = oracle.quantized_gated(gu16, I8, kind=0)
     g, u = oracle.from_bf16(gu16[:, :256]), oracle.from_bf16(gu16[:, 256:])
     assert np.abs(oracle.from_bf16(act) - g / (1 + np.exp(-g)) * u).max() < 0.03
+
+
+def _bf16(bits):
+    return (bits.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+
+
+def test_oracle_against_reference_held_fixtures(oracle):
+    """The `ref_*` arrays of the fixtures are outputs of the REFERENCE's kernels (row quantizer, CUTLASS SM80 /
+    GEMV / grouped GEMM) recorded on a B200 by tests/golden/make_golden.py --reference. INT8: bytes, scales and
+    bf16 GEMM bits equal the oracle's; FP8 bytes equal up to the sign of zero; FP8 and K-group GEMM outputs
+    within 2e-2 / 1e-2 relative (floor 1e-2 * rms) of the oracle's exact result."""
+    index = json.loads((GOLDEN / "index.json").read_text())
+    assert index.get("reference_held"), "fixtures were generated without the reference kernels"
+    for case in index["cases"]:
+        data = np.load(GOLDEN / case["file"])
+        fmt, group, rotation = case["format"], case["group"], case["rotation"]
+        for tag, source in (("x", "x16"), ("w", "w16")):
+            q, s = oracle.row_quantize(data[source], fmt, group, rotation)
+            theirs_q, theirs_s = data[f"ref_{tag}q"], data[f"ref_s{tag}"]
+            assert np.array_equal(s.ravel().view(np.uint32), theirs_s.ravel().view(np.uint32)), (case, tag)
+            differs = q != theirs_q
+            if fmt == FP8:
+                differs &= ((q | theirs_q) & 0x7F) != 0
+            assert not differs.any(), (case, tag)
+        out, exact = oracle.quant_linear(data["ref_xq"], data["ref_sx"], data["ref_wq"], data["ref_sw"], fmt, group, group,
+                                         threads=2)
+        if fmt == I8 and not group:
+            assert np.array_equal(out, data["ref_out16"]), case
+        else:
+            want = exact.astype(np.float64)
+            floor = 1e-2 * np.sqrt(np.mean(want ** 2))
+            error = np.max(np.abs(_bf16(data["ref_out16"]) - want) / np.maximum(np.abs(want), floor))
+            assert error < (2e-2 if fmt == FP8 else 1e-2) + 2.0 ** -8, (case, error)
+
+
+def test_oracle_producers_against_reference_held_fixtures(oracle):
+    """Residual + RMSNorm + quantize and SiLU-gate + quantize as the reference's kernels computed them. The residual
+    written back is exact bf16 arithmetic and must match bit for bit; the quantized rows depend on the GPU's
+    approximate rsqrt / exp, which a CPU cannot reproduce bit for bit, so bytes may differ by one step on a small
+    fraction of elements and scales by a few ulps."""
+    index = json.loads((GOLDEN / "index.json").read_text())
+    for case in index["producers"]:
+        data = np.load(GOLDEN / case["file"])
+        fmt, group, rotation = case["format"], case["group"], case["rotation"]
+        residual, _, q, s = oracle.quantized_norm(data["residual16"], data["update16"], data["weight16"].ravel(), fmt, 1e-6,
+                                                  group=group, rotation=rotation)
+        assert np.array_equal(residual, data["ref_norm_residual"]), case
+        _, gq, gs = oracle.quantized_gated(data["gate_up16"], fmt, kind=0, group=group, rotation=rotation)
+        for mine_q, mine_s, theirs_q, theirs_s in ((q, s, data["ref_norm_q"], data["ref_norm_s"]),
+                                                   (gq, gs, data["ref_gated_q"], data["ref_gated_s"])):
+            assert np.allclose(mine_s.ravel(), theirs_s.ravel(), rtol=2e-2), case
+            if fmt == I8:
+                step = np.abs(mine_q.view(np.int8).astype(np.int32) - theirs_q.view(np.int8).astype(np.int32))
+                assert step.max() <= 1 + (1 if rotation else 0) and (step > 0).mean() < 0.05, (case, step.max(), (step > 0).mean())
+            else:
+                decode = np.array([oracle.lib.oracle_fp8_e4m3_decode(v) for v in range(256)], dtype=np.float64)
+                a, b = decode[mine_q], decode[theirs_q]
+                close = np.abs(a - b) <= 0.13 * np.maximum(np.abs(a), np.abs(b)) + 2.0 ** -9  # one e4m3 step
+                assert close.mean() > 0.999 and (mine_q != theirs_q).mean() < 0.05, case
