@@ -44,7 +44,7 @@ NOMINAL_HBM_GBS, NOMINAL_TENSOR_TOPS = 8000.0, 4500.0
 # DRAM bytes (read + written) of one GEMM launch at M=64, from single-launch ncu captures of each of
 # the four layer shapes (dram__bytes_read.sum + dram__bytes_write.sum). Other row counts scale them
 # by the algorithmic bytes, which is what the traffic follows (weights dominate both).
-NCU_DRAM_BYTES_M64 = {"qkv": None, "o": None, "gate_up": 25_410_000 + 1_572_864, "down": None}
+NCU_DRAM_BYTES_M64 = {"qkv": 8_596_352, "o": 4_394_112, "gate_up": 25_406_720, "down": 13_044_992}  # the bf16 outputs stay in L2
 
 
 # ------------------------------------------------------------------------------------------------
