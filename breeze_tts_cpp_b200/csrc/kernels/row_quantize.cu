@@ -82,12 +82,65 @@ row_quantize_wide(const T *__restrict__ x, unsigned char *__restrict__ q, float 
     }
 }
 
+// Long batches with one scale per row: one WARP per row, eight rows per CTA. The row stays in the
+// lane's registers (up to 16 128-bit loads, all issued before the first use) and the amax needs only a
+// warp reduction, so no CTA-wide barrier sits between the read and the write; with thousands of rows
+// this keeps far more bytes in flight per SM than one small CTA per row. Max is exact, so the bytes
+// and scales are the same as the CTA-per-row kernel's.
+template <Type F, class T, int Loads>
+__global__ void __launch_bounds__(kThreads)
+row_quantize_warp_rows(const T *__restrict__ x, unsigned char *__restrict__ q, float *__restrict__ scales, int rows,
+                       int cols, int stride) {
+    pdl_launch_dependents();
+    pdl_wait_upstream();
+    const int row = blockIdx.x * (kThreads / 32) + int(threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const T *source = x + size_t(row) * stride;
+    uint4 raw[Loads];
+#pragma unroll
+    for (int j = 0; j < Loads; ++j) {
+        const int column = (j * 32 + lane) * 8;
+        raw[j] = column < cols ? *reinterpret_cast<const uint4 *>(source + column) : make_uint4(0, 0, 0, 0);
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < Loads; ++j) {
+        float v[8];
+        unpack8<T>(raw[j], v);
+        amax = fmaxf(amax, abs_max8(v));
+    }
+    amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax))); // non-negative floats order like their bits
+    const float step = quant_scale<F>(amax), inverse = __fdiv_rn(1.f, step);
+    if (!lane) scales[row] = step;
+#pragma unroll
+    for (int j = 0; j < Loads; ++j) {
+        const int column = (j * 32 + lane) * 8;
+        if (column < cols) {
+            float v[8];
+            unpack8<T>(raw[j], v);
+            store8<F>(q + size_t(row) * cols + column, 8, true, v, inverse);
+        }
+    }
+}
+
 template <Type F, class T, bool Rotate>
 void launch_typed(const T *x, unsigned char *q, float *scales, int rows, int cols, int stride,
                   int group, int multiprocessors, cudaStream_t stream) {
     const bool aligned = cols % 8 == 0 && stride % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
                          reinterpret_cast<uintptr_t>(q) % 8 == 0;
     const int chunks = (cols + kThreads * 8 - 1) / (kThreads * 8); // 2048-column slabs per row
+    if (!group && !Rotate && aligned && cols <= 4096 && rows >= 8 * multiprocessors) {
+        const dim3 grid(unsigned((rows + kThreads / 32 - 1) / (kThreads / 32)));
+#define B200Q_WARP_ROWS(L)                                                                                             \
+    launch_pdl("row quantize launch", row_quantize_warp_rows<F, T, L>, grid, dim3(kThreads), 0, stream, x, q, scales, rows, \
+               cols, stride)
+        const int loads = (cols + 255) / 256;
+        if (loads <= 4) B200Q_WARP_ROWS(4);
+        else if (loads <= 8) B200Q_WARP_ROWS(8);
+        else B200Q_WARP_ROWS(16);
+#undef B200Q_WARP_ROWS
+        return;
+    }
     int parts = 1;
     if (group) {
         // K groups never cross a 2048-column slab, so slabs of one row can go to different CTAs.

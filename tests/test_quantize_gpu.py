@@ -106,3 +106,28 @@ def test_row_quantize_matches_reference_kernels(reference_kernels, ctx_factory, 
     torch.cuda.synchronize()
     assert torch.equal(mine.values, theirs.values)
     assert torch.equal(mine.scales.view(torch.int32), theirs.scales.view(torch.int32))
+
+
+@pytest.mark.parametrize("fmt", [I8, FP8])
+@pytest.mark.parametrize("rows,cols,stride,type_code", [(8192, 2048, 0, BF16), (1500, 520, 0, BF16), (2000, 4096, 0, F16),
+                                                        (1300, 1024, 2048, BF16), (1187, 8, 0, BF16), (4096, 4104, 0, BF16)])
+def test_long_batches_take_the_warp_per_row_kernel(reference_kernels, ctx_factory, fmt, rows, cols, stride, type_code):
+    """Thousands of rows with one scale per row (the prefill quantizer): bytes and scales identical to the
+    reference's row quantizer, strided sources and both 16-bit types included; the last shape is one column
+    packet too wide for the warp-per-row kernel and takes the CTA-per-row one."""
+    from breeze_tts_cpp_b200 import ops
+    ctx = ctx_factory("int8" if fmt == I8 else "fp8")
+    dtype = torch.bfloat16 if type_code == BF16 else torch.float16
+    g = torch.Generator(device="cuda").manual_seed(rows + cols)
+    wide = (torch.randn(rows, stride or cols, generator=g, device="cuda") * 3).to(dtype)
+    wide[5] = 0  # an all-zero row: scale 1
+    x = wide[:, :cols]
+    mine, theirs = ops.RowScaledView.empty(rows, cols, fmt), ops.RowScaledView.empty(rows, cols, fmt)
+    ctx.quantize_rows(x, mine)
+    rc = reference_kernels.ttsref_row_quantize(x.data_ptr(), rows, cols, stride, type_code, theirs.values.data_ptr(),
+                                               theirs.scales.data_ptr(), fmt, 0, 0, None)
+    assert rc == 0, reference_kernels.ttsref_last_error()
+    torch.cuda.synchronize()
+    assert torch.equal(mine.scales.view(torch.int32), theirs.scales.view(torch.int32))
+    assert torch.equal(mine.values, theirs.values)
+    assert float(mine.scales[5]) == 1.0
