@@ -8,7 +8,7 @@ namespace tts {
 using namespace b200;
 
 // Figures measured on a B200 at 1965 MHz: 6.55 TB/s copy bandwidth; one SM pulls about 85 GB/s
-// through TMA; one `tcgen05.mma` stream per SM adds up to about 4.5 POP/s; a dependent launch costs
+// through TMA when it streams alone, about 60 GB/s inside a chain of launches; one `tcgen05.mma` stream per SM adds up to about 4.5 POP/s; a dependent launch costs
 // about 4 us that do not scale with bytes (launch boundary, arrival of the first activation tile,
 // accumulator drain and store).
 ChipModel ChipModel::b200(int multiprocessors) {
@@ -21,7 +21,7 @@ ChipModel ChipModel::b200(int multiprocessors) {
     chip.warp_tensor_ops_per_us = chip.tensor_ops_per_us / chip.sms;
     chip.warp_instructions_per_us = 4. * 1965;
     chip.cache_bytes = size_t(126) << 20;
-    chip.cache_bytes_per_us = 85e3 * chip.sms;
+    chip.cache_bytes_per_us = 60e3 * chip.sms; // per SM while the next launch of a chain prefetches too (85 GB/s alone)
     return chip;
 }
 
@@ -90,25 +90,41 @@ double linear_cost(KernelProblem p, LinearPath path, Type, const ChipModel &chip
         const double waves = std::ceil(tiles / sms);
         return chip.kernel_us + ops * (waves * sms / tiles) / (0.3 * chip.tensor_ops_per_us);
     }
-    // Weight-streaming kernel: a fixed latency plus the streaming time of the busiest SM, bounded by
-    // what one SM can pull and by its share of HBM; the split-K exchange grows with the cluster.
+    // Weight-streaming kernel, as it runs inside a decoder chain: the launch starts under programmatic
+    // dependent launch while its quantizer still runs, so by the time the activations exist the ring
+    // already holds `stages` K blocks of weights. What is left on the critical path is
+    //   * the K blocks that did not fit the ring, at what one SM can pull or its share of HBM;
+    //   * the MMAs, which cost a fixed ~0.12 us per K block up to 64 tokens (four instructions of at
+    //     least 48 tensor-pipe cycles each, however few tokens), more for wider tiles;
+    //   * the split-K exchange, about 0.3 us per CTA of the cluster at 64 tokens (less for narrower tiles); clusters of seven and eight lose
+    //     about 6 us more (their CTAs are placed late and miss the weight prefetch);
+    //   * the epilogue, about 0.4 us per 16-token pass a CTA finishes;
+    //   * a crowding term: beyond about 100 CTAs the next launch of the chain finds too few free SMs
+    //     to start its own prefetch early.
+    // Calibrated on the decoder layer's four shapes at 8 to 64 rows, timed inside the chain.
     const int splits = std::max(1, path.splits), per_split = blocks(kb_total, splits);
+    const LaunchShape shape = launch_shape(path.tokens, grouped(p), per_split, splits, group_units(p.input_group, p.weight_group));
+    if (!shape.fits) return std::numeric_limits<double>::infinity();
     const double stage_bytes = double(kBlockChannels + path.tokens) * kBlockK;
     const int64_t ctas = int64_t(blocks(p.channels, kBlockChannels)) * blocks(p.rows, path.tokens) * splits;
     // Small tiles leave room for two CTAs per SM; clusters are placed whole.
-    const LaunchShape shape = launch_shape(path.tokens, grouped(p), per_split, splits, group_units(p.input_group, p.weight_group));
-    if (!shape.fits) return std::numeric_limits<double>::infinity();
-    const int resident = (!grouped(p) && path.tokens <= 64 && shape.fits && shape.smem <= 108 * 1024) ? 2 : 1;
+    const int resident = (!grouped(p) && path.tokens <= 64 && shape.smem <= 108 * 1024) ? 2 : 1;
     const int64_t slots = std::max<int64_t>(splits, int64_t(sms) * resident / splits * splits);
     const double waves = double((ctas + slots - 1) / slots);
-    const double per_sm = chip.cache_bytes_per_us > 0 ? chip.cache_bytes_per_us / sms : 85e3;
-    const double per_sm_stream = per_split * stage_bytes / per_sm;
-    const double hbm_stream = double(std::min(ctas, slots)) * per_split * stage_bytes / (0.84 * chip.memory_bytes_per_us);
-    // Measured: the exchange costs about 0.2 us per CTA of the cluster up to four, and clusters wider
-    // than four lose about 0.8 us more per CTA (fewer of them fit a GPC, and each K slice gets too
-    // short to hide the exchange).
-    const double exchange = splits > 1 ? 0.3 + 0.2 * splits + 0.8 * std::max(0, splits - 4) : 0.0;
-    return chip.kernel_us + waves * std::max(per_sm_stream, hbm_stream) + exchange;
+    const double per_sm = chip.cache_bytes_per_us > 0 ? chip.cache_bytes_per_us / sms : 60e3;
+    const int exposed_blocks = std::max(0, per_split - shape.stages);
+    const double exposed = exposed_blocks * stage_bytes *
+                           std::max(1.0 / per_sm, double(std::min(ctas, slots)) / (0.84 * chip.memory_bytes_per_us));
+    const double mma_block = path.tokens <= 64 ? 0.12 : path.tokens <= 128 ? 0.16 : 0.29;
+    const double compute = std::max(per_split * mma_block, exposed + mma_block) * (grouped(p) ? 1.5 : 1.0);
+    const double exchange = splits > 1 ? (0.15 + 0.15 * path.tokens / 64.0) * splits + (splits > 6 ? 6.0 : 0.0) : 0.0;
+    const int passes = blocks(std::min(p.rows, path.tokens), kRowsPerPass);
+    const double epilogue = 0.4 * (splits > 1 ? blocks(passes, splits) : passes);
+    const double crowding = 0.03 * double(std::max<int64_t>(0, std::min(ctas, slots) - 100));
+    // Later waves see a cold ring: they stream all of their K blocks.
+    const double later_wave = per_split * stage_bytes * std::max(1.0 / per_sm, double(slots) / (0.84 * chip.memory_bytes_per_us)) +
+                              exchange + epilogue;
+    return chip.kernel_us + compute + exchange + epilogue + crowding + (waves - 1.0) * later_wave;
 }
 
 double linear_pipeline_cost(KernelProblem p, LinearPath path, Type format, const ChipModel &chip, LinearFinishWork finish,
