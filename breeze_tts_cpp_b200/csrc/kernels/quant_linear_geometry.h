@@ -12,7 +12,7 @@ constexpr int kRowsPerPass = 16;    // token rows the epilogue warps finish per 
 constexpr int kMaxSplits = 8;       // portable thread-block cluster size
 constexpr int kPrefillTokens = 256; // token tile of the persistent per-row kernels
 constexpr int kGroupedTokens = 128; // token tile of the persistent K-group kernel
-constexpr size_t kSmemBudget = 208 * 1024; // dynamic part per CTA; leaves room on the SM for a co-resident producer CTA of the next kernel
+constexpr size_t kSmemBudget = 224 * 1024; // dynamic part per CTA: all but 3 KiB of the SM, which is what the static barriers and a co-resident quantizer CTA of the next launch need
 
 struct LaunchShape {
     bool fits = false;
