@@ -315,22 +315,31 @@ def run_chain(args, torch, dist, rank, world, device, arm_factory):
         decode_step(arm, stack)  # eager once: lazy module loading, plans
         stream.synchronize()
         assert arm.status() == 0, "device status word set"
+        # Three graphs: the step with its input reset on the device (value), the same step fed from and
+        # read back to pinned host memory (e2e), and the GEMM launches alone (roofline).
+        host_x = stack.x0.cpu().pin_memory()
+        host_out = torch.empty(stack.rows, HIDDEN, dtype=torch.bfloat16).pin_memory()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
+            stack.x.copy_(stack.x0, non_blocking=True)
             decode_step(arm, stack)
+        e2e_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(e2e_graph, stream=stream):
+            stack.x.copy_(host_x, non_blocking=True)
+            decode_step(arm, stack)
+            host_out.copy_(stack.u, non_blocking=True)
         gemm_graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(gemm_graph, stream=stream):
             decode_step(arm, stack, gemm_only=True)
-    result = time_steps(args, torch, dist, world, device, stream, stack, graph, gemm_graph)
+    result = time_steps(args, torch, dist, world, device, stream, stack, graph, e2e_graph, gemm_graph, host_x, host_out)
     assert arm.status() == 0, "device status word set during the timed region"
     return arm, stream, result
 
 
-def time_steps(args, torch, dist, world, device, stream, stack, graph, gemm_graph):
-    """value: K graph replays with inputs resident; e2e: per step H2D of the step input, replay, D2H of the
-    step result, stream sync; roofline: K replays of the GEMM launches alone."""
-    host_x = stack.x0.cpu().pin_memory()
-    host_out = torch.empty(stack.rows, HIDDEN, dtype=torch.bfloat16).pin_memory()
+def time_steps(args, torch, dist, world, device, stream, stack, graph, e2e_graph, gemm_graph, host_x, host_out):
+    """value: K graph replays with inputs resident (the graph resets the residual stream from a device copy);
+    e2e: per step one graph that copies the step input from pinned host memory, runs the chain and copies the
+    step result back to pinned host memory, then a stream sync; roofline: K replays of the GEMM launches alone."""
 
     def barrier():
         if world > 1:
@@ -350,13 +359,10 @@ def time_steps(args, torch, dist, world, device, stream, stack, graph, gemm_grap
         return start.elapsed_time(stop)
 
     def resident_step():
-        stack.x.copy_(stack.x0, non_blocking=True)  # device-to-device reset of the residual stream
         graph.replay()
 
     def e2e_step():
-        stack.x.copy_(host_x, non_blocking=True)
-        graph.replay()
-        host_out.copy_(stack.u, non_blocking=True)
+        e2e_graph.replay()
         stream.synchronize()
 
     with torch.cuda.stream(stream):
