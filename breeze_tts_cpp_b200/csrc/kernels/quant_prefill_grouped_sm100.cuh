@@ -35,6 +35,32 @@ constexpr int kScaleSlotBytes = 2 * kGroupedTokens * 4; // sx_g slice then sw_g 
 constexpr size_t kGroupedSmem = 1024 + size_t(kGroupedStages) * (kBlockChannels + kGroupedTokens) * kBlockK +
                                 size_t(kScaleSlots) * kScaleSlotBytes + kPrefillPatchBytes;
 
+namespace ptx {
+// Two fp32 lanes in one 64-bit register, and the packed arithmetic Blackwell has for them.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+} // namespace ptx
 
 template <Type F>
 __global__ void __launch_bounds__(kGroupedThreads, 1)
@@ -162,80 +188,58 @@ w8a8_tcgen05_prefill_grouped(const __grid_constant__ CUtensorMap map_w, const __
         const float *__restrict__ residual = a.residual_f32;
         const float *scales = reinterpret_cast<const float *>(aligned + kRingBytes);
         uint16_t *patches = reinterpret_cast<uint16_t *>(aligned + kRingBytes + kScaleBytes);
-        const float2 magic2 = make_float2(-12582912.f, -12582912.f);
+        const uint64_t magic2 = ptx::pack2(-12582912.f, -12582912.f);
         ptx::wait_for_upstream();
         uint32_t count = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
             const int n0 = (tile % n_tiles) * kBlockChannels, m0 = (tile / n_tiles) * BN;
             const int valid_tokens = min(BN, a.m - m0);
-            float2 result[32]; // [chunk 0..3][pair 0..7]: tokens (2*k + half)*16 + 2*pair, +1
+            uint64_t result[32]; // [chunk 0..3][pair 0..7]: tokens (2*k + half)*16 + 2*pair, +1
 #pragma unroll
-            for (int i = 0; i < 32; ++i) result[i] = make_float2(0.f, 0.f);
-            // One 16-token chunk of this thread's channel: result += float(p) * (sx * sw), two tokens per
-            // packed fp32 instruction. INT8 partials become floats exactly by the magic-constant trick
-            // (bits(2^23 + 2^22 + p) read as fp32, minus that constant; |p| <= 128 * 127^2 < 2^22).
-            auto rescale = [&](int k, const uint32_t (&r)[16], const float *slot_scales, float2 scale_w2) {
-                const float4 *sx4 = reinterpret_cast<const float4 *>(slot_scales + (2 * k + half) * 16);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float4 sx = sx4[q];
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int i = 4 * q + 2 * h;
-                        float2 p;
-                        if (kInt) p = __fadd2_rn(make_float2(__uint_as_float(r[i] + 0x4B400000u), __uint_as_float(r[i + 1] + 0x4B400000u)), magic2);
-                        else p = make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-                        const float2 scale = __fmul2_rn(h ? make_float2(sx.z, sx.w) : make_float2(sx.x, sx.y), scale_w2);
-                        result[k * 8 + i / 2] = __ffma2_rn(p, scale, result[k * 8 + i / 2]);
-                    }
-                }
-            };
-            auto chunk_address = [&](uint32_t buffer, int k) { return lane_base + buffer * uint32_t(BN) + uint32_t((2 * k + half) * 16); };
-            // The tensor-memory load of the next chunk is always in flight while a chunk is rescaled: the
-            // four chunks of a K block alternate between two register sets, and the first chunk of the
-            // next K block is requested before the last chunk of this one is rescaled.
-            uint32_t r0[16], r1[16];
-            if (!ptx::mbar_wait(ptx::smem_u32(&acc_full[count % kGroupedAccumulators]), (count / kGroupedAccumulators) & 1u, abort_ptr)) ok = false;
-            if (ok) {
-                ptx::tcgen05_fence_after();
-                ptx::tmem_load16(chunk_address(count % kGroupedAccumulators, 0), r0);
-            }
+            for (int i = 0; i < 32; ++i) result[i] = 0ull;
 #pragma unroll 1
-            for (int kb = 0; kb < kb_count && ok; ++kb, ++count) {
-                const uint32_t buffer = count % kGroupedAccumulators;
+            for (int kb = 0; kb < kb_count; ++kb, ++count) {
+                const uint32_t buffer = count % kGroupedAccumulators, use = (count / kGroupedAccumulators) & 1u;
                 const uint32_t slot = count % kScaleSlots, slot_use = (count / kScaleSlots) & 1u;
-                if (!ptx::mbar_wait(ptx::smem_u32(&scale_full[slot]), slot_use, abort_ptr)) { ok = false; break; }
-                const float *slot_scales = scales + slot * (kScaleSlotBytes / 4);
-                const float scale_w = slot_scales[BN + quadrant * 32 + lane];
-                const float2 scale_w2 = make_float2(scale_w, scale_w);
+                if (!ptx::mbar_wait(ptx::smem_u32(&acc_full[buffer]), use, abort_ptr)) { ok = false; break; }
+                ptx::tcgen05_fence_after();
+                uint32_t r[4][16];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) ptx::tmem_load16(lane_base + buffer * uint32_t(BN) + uint32_t((2 * k + half) * 16), r[k]);
                 ptx::tmem_load_wait();
-                ptx::tmem_load16(chunk_address(buffer, 1), r1);
-                rescale(0, r0, slot_scales, scale_w2);
-                ptx::tmem_load_wait();
-                ptx::tmem_load16(chunk_address(buffer, 2), r0);
-                rescale(1, r1, slot_scales, scale_w2);
-                ptx::tmem_load_wait();
-                ptx::tmem_load16(chunk_address(buffer, 3), r1);
-                rescale(2, r0, slot_scales, scale_w2);
-                ptx::tmem_load_wait();
-                // The whole accumulator is in registers: the tensor cores may have the buffer back.
+                // Everything is in registers: the tensor cores may have the buffer back.
                 ptx::tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&acc_empty[buffer]));
-                if (kb + 1 < kb_count) {
-                    const uint32_t next = count + 1;
-                    if (!ptx::mbar_wait(ptx::smem_u32(&acc_full[next % kGroupedAccumulators]), (next / kGroupedAccumulators) & 1u, abort_ptr)) ok = false;
-                    if (ok) {
-                        ptx::tcgen05_fence_after();
-                        ptx::tmem_load16(chunk_address(next % kGroupedAccumulators, 0), r0);
+                if (!ptx::mbar_wait(ptx::smem_u32(&scale_full[slot]), slot_use, abort_ptr)) { ok = false; break; }
+                const float *slot_scales = scales + slot * (kScaleSlotBytes / 4);
+                const float scale_w = slot_scales[BN + quadrant * 32 + lane];
+                const uint64_t scale_w2 = ptx::pack2(scale_w, scale_w);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float4 *sx4 = reinterpret_cast<const float4 *>(slot_scales + (2 * k + half) * 16);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 sx = sx4[q];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int i = 4 * q + 2 * h;
+                            uint64_t p;
+                            if (kInt) {
+                                // float(int) exactly: bits(2^23 + 2^22 + p) read as fp32, minus that constant.
+                                p = ptx::add2(ptx::pack2(__uint_as_float(r[k][i] + 0x4B400000u), __uint_as_float(r[k][i + 1] + 0x4B400000u)), magic2);
+                            } else {
+                                p = ptx::pack2(__uint_as_float(r[k][i]), __uint_as_float(r[k][i + 1]));
+                            }
+                            const uint64_t s = ptx::mul2(h ? ptx::pack2(sx.z, sx.w) : ptx::pack2(sx.x, sx.y), scale_w2);
+                            result[k * 8 + i / 2] = ptx::fma2(p, s, result[k * 8 + i / 2]);
+                        }
                     }
                 }
-                rescale(3, r1, slot_scales, scale_w2);
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&scale_empty[slot]));
             }
-            ptx::tmem_load_wait(); // nothing may still be in flight on an early exit
             // All eight warps decide together whether the tile is stored (a warp that left alone would
             // strand the three that share its staging patch); the same barrier keeps two consecutive
             // tiles from meeting in one patch.
@@ -249,8 +253,10 @@ w8a8_tcgen05_prefill_grouped(const __grid_constant__ CUtensorMap map_w, const __
                     uint32_t words[16];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        words[2 * j] = __float_as_uint(result[k * 8 + j].x);
-                        words[2 * j + 1] = __float_as_uint(result[k * 8 + j].y);
+                        float lo, hi;
+                        ptx::unpack2(result[k * 8 + j], lo, hi);
+                        words[2 * j] = __float_as_uint(lo);
+                        words[2 * j + 1] = __float_as_uint(hi);
                     }
                     prefill_store_chunk<false>(a, words, ones, 1.f, residual, m0 + chunk * 16, n0, valid_tokens - chunk * 16,
                                                quadrant, lane, half, patches + ((half * 2 + (k & 1)) * 16 * kBlockChannels));
