@@ -203,11 +203,14 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             // (one barrier per stage), then wait for upstream and add the activation tiles of all
             // those stages under ONE barrier. A barrier test between MMA issues costs the issuing
             // thread about 200 cycles, so the burst over the prefetched stages must not need any.
+            // Weights are streamed once: they are marked first-to-evict so that the few megabytes of
+            // activations the chain keeps passing from kernel to kernel stay in L2.
+            const uint64_t stream_once = ptx::policy_evict_first();
             const int ahead = min(a.stages, kb_count);
             for (int i = 0; i < ahead; ++i) {
                 const uint32_t bar = ptx::smem_u32(&full_bar[i]);
                 ptx::mbar_arrive_expect_tx(bar, kWeightBytes + (i == 0 ? uint32_t(a.expiry_extra_bytes) : 0u));
-                ptx::tma_load_2d(tiles_base + uint32_t(i) * kStageBytes, &map_w, bar, (kb_begin + i) * kBlockK, n0);
+                ptx::tma_load_2d_hint(tiles_base + uint32_t(i) * kStageBytes, &map_w, bar, (kb_begin + i) * kBlockK, n0, stream_once);
             }
             ptx::wait_for_upstream();
             ptx::mbar_arrive_expect_tx(ptx::smem_u32(&x_full), uint32_t(ahead) * kTokenBytes);
@@ -221,7 +224,7 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 const uint32_t bar = ptx::smem_u32(&full_bar[stage]);
                 const uint32_t dst = tiles_base + uint32_t(stage) * kStageBytes;
                 ptx::mbar_arrive_expect_tx(bar, kStageBytes);
-                ptx::tma_load_2d(dst, &map_w, bar, kb * kBlockK, n0);
+                ptx::tma_load_2d_hint(dst, &map_w, bar, kb * kBlockK, n0, stream_once);
                 ptx::tma_load_2d(dst + kWeightBytes, &map_x, bar, kb * kBlockK, m0);
                 if (++stage == a.stages) { stage = 0; phase ^= 1u; }
             }

@@ -117,7 +117,7 @@ double linear_cost(KernelProblem p, LinearPath path, Type, const ChipModel &chip
                            std::max(1.0 / per_sm, double(std::min(ctas, slots)) / (0.84 * chip.memory_bytes_per_us));
     const double mma_block = path.tokens <= 64 ? 0.12 : path.tokens <= 128 ? 0.16 : 0.29;
     const double compute = std::max(per_split * mma_block, exposed + mma_block) * (grouped(p) ? 1.5 : 1.0);
-    const double exchange = splits > 1 ? (0.15 + 0.15 * path.tokens / 64.0) * splits + (splits > 6 ? 6.0 : 0.0) : 0.0;
+    const double exchange = splits > 1 ? (0.17 + 0.15 * path.tokens / 64.0) * splits + (splits > 6 ? 6.0 : 0.0) : 0.0;
     const int passes = blocks(std::min(p.rows, path.tokens), kRowsPerPass);
     const double epilogue = 0.4 * (splits > 1 ? blocks(passes, splits) : passes);
     const double crowding = 0.03 * double(std::max<int64_t>(0, std::min(ctas, slots) - 100));
