@@ -99,8 +99,8 @@ double linear_cost(KernelProblem p, LinearPath path, Type, const ChipModel &chip
     //   * the split-K exchange, about 0.3 us per CTA of the cluster at 64 tokens (less for narrower tiles); clusters of seven and eight lose
     //     about 6 us more (their CTAs are placed late and miss the weight prefetch);
     //   * the epilogue, about 0.4 us per 16-token pass a CTA finishes;
-    //   * a crowding term: beyond about 100 CTAs the next launch of the chain finds too few free SMs
-    //     to start its own prefetch early.
+    //   * a crowding term: the more SMs a launch holds, the fewer the next launch of the chain finds
+    //     free to start its own prefetch early; uneven K splits cost a little as well.
     // Calibrated on the decoder layer's four shapes at 8 to 64 rows, timed inside the chain.
     const int splits = std::max(1, path.splits), per_split = blocks(kb_total, splits);
     const LaunchShape shape = launch_shape(path.tokens, grouped(p), per_split, splits, group_units(p.input_group, p.weight_group));
@@ -117,10 +117,10 @@ double linear_cost(KernelProblem p, LinearPath path, Type, const ChipModel &chip
                            std::max(1.0 / per_sm, double(std::min(ctas, slots)) / (0.84 * chip.memory_bytes_per_us));
     const double mma_block = path.tokens <= 64 ? 0.12 : path.tokens <= 128 ? 0.16 : 0.29;
     const double compute = std::max(per_split * mma_block, exposed + mma_block) * (grouped(p) ? 1.5 : 1.0);
-    const double exchange = splits > 1 ? (0.17 + 0.15 * path.tokens / 64.0) * splits + (splits > 6 ? 6.0 : 0.0) : 0.0;
+    const double exchange = splits > 1 ? (0.15 + 0.15 * path.tokens / 64.0) * splits + (kb_total % splits ? 0.15 : 0.0) + (splits > 6 ? 6.0 : 0.0) : 0.0;
     const int passes = blocks(std::min(p.rows, path.tokens), kRowsPerPass);
     const double epilogue = 0.4 * (splits > 1 ? blocks(passes, splits) : passes);
-    const double crowding = 0.03 * double(std::max<int64_t>(0, std::min(ctas, slots) - 100));
+    const double crowding = 0.01 * double(std::max<int64_t>(0, std::min(ctas, slots) - 64));
     // Later waves see a cold ring: they stream all of their K blocks.
     const double later_wave = per_split * stage_bytes * std::max(1.0 / per_sm, double(slots) / (0.84 * chip.memory_bytes_per_us)) +
                               exchange + epilogue;
