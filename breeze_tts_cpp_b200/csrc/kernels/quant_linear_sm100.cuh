@@ -103,7 +103,7 @@ __device__ __noinline__ float finish_chain(const FusedEpilogue &e, int type, flo
     value = round_to(value, type);
     if (e.bias) value = round_to(__fadd_rn(value, bias), type);
     if (e.residual || e.value_scale != 1.f)
-        value = round_to(__fadd_rn(__fmul_rn(e.value_scale, value), __fmul_rn(e.residual_scale, skip)), type);
+        value = round_to(__fmaf_rn(e.value_scale, value, __fmul_rn(e.residual_scale, skip)), type); // contracted as in the reference's finishing pass
     if (e.activation || e.output_scale != 1.f)
         value = activate(round_to(__fmul_rn(value, e.output_scale), type), e.activation, e.alpha);
     return value;

@@ -3,7 +3,7 @@
 // to the storage type exactly where the reference rounds
 // (src/ops/kernels/sequence/sequence_internal.cuh:31-74, activations
 // src/ops/kernels/common/activation.cuh:5-27). Shared by the separate finishing pass and by the
-// finish-and-quantize pass. Every product and sum is an explicit round-to-nearest operation.
+// finish-and-quantize pass. Every product, sum and fused multiply-add is written out explicitly.
 #pragma once
 #include "ops/epilogue.h"
 #include <cuda_bf16.h>
@@ -52,10 +52,11 @@ __device__ __forceinline__ float finish_activation(float x, int kind, float alph
     case 3: return __fdiv_rn(x, __fadd_rn(1.f, expf(-x)));
     case 4: return __fmul_rn(__fmul_rn(.5f, x), __fadd_rn(1.f, erff(__fmul_rn(x, .7071067811865475f))));
     case 5: {
-        const float cube = __fmul_rn(__fmul_rn(__fmul_rn(.044715f, x), x), x);
-        // The hardware's approximate tanh, as in the reference's finishing pass (activation.cuh:16-17).
+        // The reference's finishing pass is compiled with multiply-add contraction: the cubic term and x meet
+        // in one fused operation. The hardware's approximate tanh as there (activation.cuh:16-17).
+        const float inner = __fmaf_rn(__fmul_rn(__fmul_rn(.044715f, x), x), x, x);
         float t;
-        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(__fmul_rn(.7978845608028654f, __fadd_rn(x, cube))));
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(__fmul_rn(.7978845608028654f, inner)));
         return __fmul_rn(__fmul_rn(.5f, x), __fadd_rn(1.f, t));
     }
     case 6: return __fmul_rn(x, tanhf(x > 20.f ? x : log1pf(expf(x))));
@@ -92,7 +93,10 @@ __device__ __forceinline__ float finish_apply(const FinishArgs &f, const FinishR
     float skip = 0.f;
     if (f.residual.data && r.residual >= 0)
         skip = r.residual < f.residual.rows ? f.residual.template get<T>(r.residual, col) : nanf("");
-    value = round_storage<T>(__fadd_rn(__fmul_rn(f.value_scale, value), __fmul_rn(f.residual_scale, skip)));
+    // The reference's finishing pass is built with multiply-add contraction: `value_scale * value + scale * skip`
+    // is one product rounded, then a fused multiply-add (found by comparing with its kernels on scales that
+    // are not powers of two).
+    value = round_storage<T>(__fmaf_rn(f.value_scale, value, __fmul_rn(f.residual_scale, skip)));
     if (f.condition.data) value = round_storage<T>(__fadd_rn(value, f.condition.template get<T>(r.sequence, col)));
     if (raw) *raw = T(value);
     return finish_activation(round_storage<T>(__fmul_rn(value, f.output_scale)), f.activation, f.alpha);

@@ -62,7 +62,7 @@ __device__ __forceinline__ void finish8(const FinishArgs &f, const FinishRow &r,
     for (int i = 0; i < 8; ++i) {
         float value = round_storage<T>(__fadd_rn(x[i], bias[i]));
         if (f.gate.data) value = round_storage<T>(__fmul_rn(value, gate[i]));
-        value = round_storage<T>(__fadd_rn(__fmul_rn(f.value_scale, value), __fmul_rn(f.residual_scale, skip[i])));
+        value = round_storage<T>(__fmaf_rn(f.value_scale, value, __fmul_rn(f.residual_scale, skip[i])));
         if (f.condition.data) value = round_storage<T>(__fadd_rn(value, condition[i]));
         before[i] = value;
         out[i] = finish_activation(round_storage<T>(__fmul_rn(value, f.output_scale)), f.activation, f.alpha);

@@ -267,7 +267,8 @@ void oracle_quant_linear(const uint8_t *xq, const float *sx, const uint8_t *wq, 
                     if (ep->bias) { value = stored + load16(ep->bias[j], output_type); stored = round16(value, output_type); }
                     if (ep->residual || ep->value_scale != 1.f) {
                         float skip = ep->residual ? load16(ep->residual[at], output_type) : 0.f;
-                        value = ep->value_scale * stored + ep->residual_scale * skip;
+                        // the reference's finishing pass contracts this into product + fused multiply-add
+                        value = std::fma(ep->value_scale, stored, ep->residual_scale * skip);
                         stored = round16(value, output_type);
                     }
                     if (ep->activation || ep->output_scale != 1.f) {
@@ -351,6 +352,191 @@ void oracle_quantized_gated(const uint16_t *input, int rows, int width, int type
         }
         if (rotation) rotate_row(row.data(), width);
         encode_row(row.data(), r, rows, width, values, scales, format, group);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The row-wise operators around the projections.
+//
+// reference: Finish::apply, src/ops/kernels/sequence/sequence_internal.cuh:52-74. Every step is
+// rounded to the storage type; `value_scale * value + scale * skip` is one rounded product and a
+// fused multiply-add (that file is built with contraction on). The transcendental activations use
+// libm here and device intrinsics there (tanh-GELU: the hardware's approximate tanh), which is why
+// they are compared with a tolerance.
+namespace {
+inline float operand(const uint16_t *base, int rows, int row, int col, int cols, int type) {
+    return base ? load16(base[size_t(rows == 1 ? 0 : row) * cols + col], type) : 0.f;
+}
+float finish_apply(const oracle_finish &f, int type, float value, int row, int col, int cols) {
+    uint16_t *raw = f.raw ? f.raw + size_t(row) * cols + col : nullptr;
+    const int per_sequence = std::max(1, f.rows_per_sequence);
+    if (f.valid_rows_per_sequence && row % per_sequence >= f.valid_rows_per_sequence) {
+        if (raw) *raw = store16(0.f, type);
+        return 0.f;
+    }
+    const int sequence = row / per_sequence;
+    value = round16(value + operand(f.bias, 1, 0, col, cols, type), type);
+    if (f.gate) value = round16(value * operand(f.gate, f.gate_rows, sequence, col, cols, type), type);
+    const int r = f.residual_index ? f.residual_index[row] : row;
+    float skip = 0.f;
+    if (f.residual && r >= 0) skip = r < f.residual_rows ? operand(f.residual, f.residual_rows, r, col, cols, type) : std::nanf("");
+    value = round16(std::fma(f.value_scale, value, f.residual_scale * skip), type);
+    if (f.condition) value = round16(value + operand(f.condition, f.condition_rows, sequence, col, cols, type), type);
+    if (raw) *raw = store16(value, type);
+    return activate(round16(value * f.output_scale, type), f.activation, f.alpha);
+}
+// Sum of 256 per-thread partials in the order of a block reduction made of warp shuffle-down trees
+// (distances 1, 2, 4, 8, 16) followed by thread 0 adding the eight warp results in order.
+float block_sum_256(const float *thread_value) {
+    float total = 0.f;
+    for (int w = 0; w < 8; ++w) {
+        float lane[32];
+        for (int l = 0; l < 32; ++l) lane[l] = thread_value[w * 32 + l];
+        for (int d = 1; d < 32; d *= 2) {
+            float next[32];
+            for (int l = 0; l < 32; ++l) next[l] = (l + d < 32 ? lane[l + d] : lane[l]) + lane[l];
+            std::memcpy(lane, next, sizeof(lane));
+        }
+        total = w ? total + lane[0] : lane[0];
+    }
+    return total;
+}
+// reference: NormRow::load / ::transform and the statistics of norm_kernel,
+// src/ops/kernels/sequence/sequence_norm.cu:36-57, 64-204. Thread t of 256 owns columns t, t+256, ...;
+// the variance accumulates fma(delta, delta, sum); the CPU's 1/sqrt stands in for rsqrtf.
+struct NormRowOracle {
+    const oracle_norm &n;
+    const uint16_t *input;
+    int row, sequence, cols, type;
+    NormRowOracle(const oracle_norm &n, const uint16_t *x, int x_rows, int row, int cols, int type)
+        : n(n), input(x + size_t(x_rows == 1 ? 0 : row) * cols), row(row), sequence(row / std::max(1, n.rows_per_sequence)),
+          cols(cols), type(type) {}
+    float load(int c) const {
+        float value = round16(load16(input[c], type) + operand(n.projection_bias, 1, 0, c, cols, type), type);
+        if (n.gate) value = round16(value * operand(n.gate, n.gate_rows, sequence, c, cols, type), type);
+        return round16(value + operand(n.residual, n.residual_rows, row, c, cols, type), type);
+    }
+    float transform(int c, float value, float mean, float inverse) const {
+        value = (value - mean) * inverse;
+        if (n.weight) value = value * load16(n.weight[c], type);
+        value = round16(value + operand(n.bias, 1, 0, c, cols, type), type);
+        if (n.scale) value = round16(value * round16(1.f + operand(n.scale, n.scale_rows, sequence, c, cols, type), type), type);
+        return round16(value + operand(n.shift, n.shift_rows, sequence, c, cols, type), type);
+    }
+    void statistics(std::vector<float> &loaded, float &mean, float &inverse) const {
+        loaded.resize(cols);
+        float partial[256];
+        for (int t = 0; t < 256; ++t) {
+            float sum = 0.f;
+            for (int c = t; c < cols; c += 256) { loaded[c] = load(c); sum += loaded[c]; }
+            partial[t] = sum;
+        }
+        mean = block_sum_256(partial) / float(cols);
+        for (int t = 0; t < 256; ++t) {
+            float sum = 0.f;
+            for (int c = t; c < cols; c += 256) { float delta = loaded[c] - mean; sum = std::fma(delta, delta, sum); }
+            partial[t] = sum;
+        }
+        inverse = 1.f / std::sqrt(block_sum_256(partial) / float(cols) + n.eps);
+    }
+};
+} // namespace
+
+// reference: pointwise, src/ops/kernels/sequence/sequence_pointwise.cu:332-357 (dense rows).
+void oracle_pointwise(const uint16_t *x, int x_rows, int rows, int cols, int type, const oracle_finish *f, uint16_t *y) {
+    const int repeat = std::max(1, f->input_repeat);
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < cols; ++c) {
+            float value = load16(x[size_t(x_rows == 1 ? 0 : r / repeat) * cols + c], type);
+            y[size_t(r) * cols + c] = store16(finish_apply(*f, type, value, r, c, cols), type);
+        }
+}
+
+// reference: pointwise_quantize_kernel, sequence_pointwise.cu:149-265: the finished row, rounded to
+// storage (and kept in `retained`), goes through the producers' common quantizing tail.
+void oracle_pointwise_quantize(const uint16_t *x, int x_rows, int rows, int cols, int type, const oracle_finish *f,
+                               uint16_t *retained, uint8_t *values, float *scales, int format, int group, int rotation) {
+    const int repeat = std::max(1, f->input_repeat);
+    std::vector<float> row(cols);
+    for (int r = 0; r < rows; ++r) {
+        for (int c = 0; c < cols; ++c) {
+            float value = load16(x[size_t(x_rows == 1 ? 0 : r / repeat) * cols + c], type);
+            row[c] = round16(finish_apply(*f, type, value, r, c, cols), type);
+            if (retained) retained[size_t(r) * cols + c] = store16(row[c], type);
+        }
+        if (rotation) rotate_row(row.data(), cols);
+        encode_row(row.data(), r, rows, cols, values, scales, format, group);
+    }
+}
+
+// reference: norm_kernel<T, RowOutput>, sequence_norm.cu:64-204, launcher :412-440. `source_rows` (optional)
+// gathers input rows; every index must be valid here.
+void oracle_layer_norm_quantize(const uint16_t *x, int x_rows, int rows, int cols, int type, const oracle_norm *n,
+                                uint16_t *normalized, uint16_t *raw, uint8_t *values, float *scales, int format, int group,
+                                int rotation) {
+    std::vector<float> loaded, row(cols);
+    for (int out = 0; out < rows; ++out) {
+        const int source = n->source_rows ? n->source_rows[out] : out;
+        NormRowOracle fusion(*n, x, x_rows, source, cols, type);
+        float mean, inverse;
+        fusion.statistics(loaded, mean, inverse);
+        for (int c = 0; c < cols; ++c) {
+            row[c] = fusion.transform(c, loaded[c], mean, inverse);
+            if (raw) raw[size_t(out) * cols + c] = store16(loaded[c], type);
+            if (normalized) normalized[size_t(out) * cols + c] = store16(row[c], type);
+        }
+        if (rotation) rotate_row(row.data(), cols);
+        encode_row(row.data(), out, rows, cols, values, scales, format, group);
+    }
+}
+
+// reference: norm_project_kernel<T, QuantProjection>, sequence_norm.cu:261-370, launcher :518-575 (K <= 512,
+// per-row scales). INT8 dot products are exact; FP8 ones are added by 32 lanes that stride K four bytes at a
+// time, fused multiply-add per element, then a shuffle-down tree 16, 8, 4, 2, 1; the result is
+// ((acc * sw[n]) * step), rounded to storage and finished.
+void oracle_normalized_linear(const uint16_t *x, int rows, int cols, int type, const oracle_norm *n, const uint8_t *wq,
+                              const float *sw, int channels, int format, const oracle_finish *f, uint16_t *out,
+                              uint8_t *encoded, float *encoded_scales, uint16_t *normalized, uint16_t *raw) {
+    std::vector<float> loaded, rounded(cols), activation(cols);
+    std::vector<uint8_t> bytes(cols);
+    for (int r = 0; r < rows; ++r) {
+        NormRowOracle fusion(*n, x, rows, r, cols, type);
+        float mean, inverse, amax = 0.f;
+        fusion.statistics(loaded, mean, inverse);
+        for (int c = 0; c < cols; ++c) {
+            rounded[c] = fusion.transform(c, loaded[c], mean, inverse);
+            amax = std::fmax(amax, std::fabs(rounded[c]));
+            if (raw) raw[size_t(r) * cols + c] = store16(loaded[c], type);
+            if (normalized) normalized[size_t(r) * cols + c] = store16(rounded[c], type);
+        }
+        const float step = oracle_scale(amax, format), reciprocal = 1.f / step;
+        if (encoded_scales) encoded_scales[r] = step;
+        for (int c = 0; c < cols; ++c) {
+            bytes[c] = encode(rounded[c] * reciprocal, format);
+            activation[c] = decode(bytes[c], format);
+            if (encoded) encoded[size_t(r) * cols + c] = bytes[c];
+        }
+        for (int j = 0; j < channels; ++j) {
+            const uint8_t *w = wq + size_t(j) * cols;
+            float result;
+            if (format == I8) {
+                int32_t acc = 0;
+                for (int c = 0; c < cols; ++c) acc += int32_t(int8_t(bytes[c])) * int32_t(int8_t(w[c]));
+                result = (float(acc) * sw[j]) * step;
+            } else {
+                float lane[32];
+                for (int l = 0; l < 32; ++l) {
+                    float acc = 0.f;
+                    for (int c = l * 4; c < cols; c += 128)
+                        for (int i = 0; i < 4 && c + i < cols; ++i) acc = std::fma(activation[c + i], decode(w[c + i], format), acc);
+                    lane[l] = acc;
+                }
+                for (int d = 16; d; d /= 2)
+                    for (int l = 0; l + d < 32 && l < d; ++l) lane[l] = lane[l] + lane[l + d];
+                result = (lane[0] * sw[j]) * step;
+            }
+            out[size_t(r) * channels + j] = store16(finish_apply(*f, type, round16(result, type), r, j, channels), type);
+        }
     }
 }
 

@@ -4,10 +4,12 @@
  * Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline leg may load it; the product
  * library never does.
  *
- * PARITY UNPINNED by the reference's own tests: the reference ships no tests, golden vectors or
- * known-answer fixtures for this path. The pins are (1) hand-derived known answers in
- * tests/test_oracle.py, (2) committed fixtures under tests/golden/, and (3) the reference's own
- * kernels built into oracle/_ref/libttsref.so and run beside this oracle on the same GPU inputs.
+ * Pinned by outputs of the reference itself: the reference ships no tests, golden vectors or
+ * known-answer fixtures for this path, so (1) the reference's own kernels are built from its sources
+ * into oracle/_ref/libttsref.so and run beside this oracle on the same inputs (GPU tests), (2) their
+ * outputs are stored beside the oracle's in the fixtures under tests/golden/ (`ref_*` keys, written by
+ * tests/golden/make_golden.py --reference) and checked on the CPU, and (3) hand-derived known
+ * answers in tests/test_oracle.py cover the scalar rules.
  *
  * Types are passed as the integer values of the reference's `tts::Type`
  * (src/core/tensor.h:8): BF16=0, F32=1, I32=2, FP8=3, I8=4, F16=5.
@@ -69,6 +71,45 @@ void oracle_quantized_norm(uint16_t *residual, const uint16_t *update, const uin
 void oracle_quantized_gated(const uint16_t *input, int rows, int width, int type, int kind,
                             uint16_t *activated, uint8_t *values, float *scales, int format, int group,
                             int rotation);
+
+/* The epilogue chain of the row-wise operators (reference ops::Epilogue, src/ops/sequence.h:8-27). Operands are dense
+ * [rows, cols] arrays of the storage type; an operand with one row broadcasts. */
+typedef struct {
+    const uint16_t *bias;            /* [cols] */
+    const uint16_t *gate;            /* [gate_rows, cols], indexed by sequence */
+    const uint16_t *residual;        /* [residual_rows, cols] */
+    const uint16_t *condition;       /* [condition_rows, cols], indexed by sequence */
+    uint16_t *raw;                   /* [rows, cols]: receives the value before the activation */
+    const int32_t *residual_index;   /* [rows]: row of `residual` each output row adds (-1 = none) */
+    int gate_rows, residual_rows, condition_rows;
+    int rows_per_sequence, valid_rows_per_sequence, input_repeat;
+    float value_scale, residual_scale, output_scale, alpha;
+    int activation;
+} oracle_finish;
+/* y[r] = finish(x[r / input_repeat]). */
+void oracle_pointwise(const uint16_t *x, int x_rows, int rows, int cols, int type, const oracle_finish *finish, uint16_t *y);
+/* finish, round to storage (kept in `retained` when given), then quantize the row. */
+void oracle_pointwise_quantize(const uint16_t *x, int x_rows, int rows, int cols, int type, const oracle_finish *finish,
+                               uint16_t *retained, uint8_t *values, float *scales, int format, int group, int rotation);
+
+/* LayerNorm with the reference's row fusion (reference ops::NormFusion, src/ops/sequence.h:29-37). */
+typedef struct {
+    const uint16_t *weight, *bias;           /* [cols] */
+    const uint16_t *projection_bias;         /* [cols], added to the input first */
+    const uint16_t *residual;                /* [residual_rows, cols] */
+    const uint16_t *gate, *scale, *shift;    /* [*_rows, cols], indexed by sequence */
+    int residual_rows, gate_rows, scale_rows, shift_rows;
+    int rows_per_sequence;
+    const int32_t *source_rows;              /* [rows]: gathers input rows (layer_norm_quantize only) */
+    float eps;
+} oracle_norm;
+void oracle_layer_norm_quantize(const uint16_t *x, int x_rows, int rows, int cols, int type, const oracle_norm *norm,
+                                uint16_t *normalized, uint16_t *raw, uint8_t *values, float *scales, int format, int group,
+                                int rotation);
+/* LayerNorm + per-row quantize + projection by wq[channels, cols] (per-channel scales sw) + finish, K <= 512. */
+void oracle_normalized_linear(const uint16_t *x, int rows, int cols, int type, const oracle_norm *norm, const uint8_t *wq,
+                              const float *sw, int channels, int format, const oracle_finish *finish, uint16_t *out,
+                              uint8_t *encoded, float *encoded_scales, uint16_t *normalized, uint16_t *raw);
 
 /* Timed scalar host-core baseline: quantize + GEMM + dequant of one linear, `threads` threads.
  * Only the first `n_slice` channels are computed (n_slice == n for the whole matrix).

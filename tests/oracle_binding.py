@@ -20,8 +20,33 @@ class OracleEpilogue(C.Structure):
                 ("activation", C.c_int), ("alpha", C.c_float)]
 
 
+class OracleFinish(C.Structure):
+    _fields_ = [("bias", C.c_void_p), ("gate", C.c_void_p), ("residual", C.c_void_p), ("condition", C.c_void_p),
+                ("raw", C.c_void_p), ("residual_index", C.c_void_p), ("gate_rows", C.c_int), ("residual_rows", C.c_int),
+                ("condition_rows", C.c_int), ("rows_per_sequence", C.c_int), ("valid_rows_per_sequence", C.c_int),
+                ("input_repeat", C.c_int), ("value_scale", C.c_float), ("residual_scale", C.c_float),
+                ("output_scale", C.c_float), ("alpha", C.c_float), ("activation", C.c_int)]
+
+
+class OracleNorm(C.Structure):
+    _fields_ = [("weight", C.c_void_p), ("bias", C.c_void_p), ("projection_bias", C.c_void_p), ("residual", C.c_void_p),
+                ("gate", C.c_void_p), ("scale", C.c_void_p), ("shift", C.c_void_p), ("residual_rows", C.c_int),
+                ("gate_rows", C.c_int), ("scale_rows", C.c_int), ("shift_rows", C.c_int), ("rows_per_sequence", C.c_int),
+                ("source_rows", C.c_void_p), ("eps", C.c_float)]
+
+
 def _ptr(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _rows2d(a):
+    """(contiguous uint16 [rows, cols] array or None, rows)."""
+    if a is None:
+        return None, 0
+    a = np.ascontiguousarray(a, dtype=np.uint16)
+    if a.ndim == 1:
+        a = a.reshape(1, -1)
+    return a, a.shape[0]
 
 
 class Oracle:
@@ -54,6 +79,14 @@ class Oracle:
                                               C.c_int]
         lib.oracle_quantized_gated.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                                C.c_void_p, C.c_int, C.c_int, C.c_int]
+        finish, norm = C.POINTER(OracleFinish), C.POINTER(OracleNorm)
+        lib.oracle_pointwise.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, finish, C.c_void_p]
+        lib.oracle_pointwise_quantize.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, finish, C.c_void_p, C.c_void_p,
+                                                  C.c_void_p, C.c_int, C.c_int, C.c_int]
+        lib.oracle_layer_norm_quantize.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, norm, C.c_void_p, C.c_void_p,
+                                                   C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+        lib.oracle_normalized_linear.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, norm, C.c_void_p, C.c_void_p, C.c_int,
+                                                 C.c_int, finish, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         lib.oracle_time_linear.restype = C.c_double
         lib.oracle_time_linear.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                            C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int]
@@ -124,6 +157,91 @@ class Oracle:
         self.lib.oracle_quantized_gated(_ptr(np.ascontiguousarray(input16)), rows, width, type_, kind, _ptr(activated),
                                         _ptr(values), _ptr(scales), fmt, group, rotation)
         return activated, values, scales
+
+
+    # ---- the row-wise operators (16-bit operands as uint16 bit patterns) ------------------------------
+    @staticmethod
+    def _finish(rows, cols, keep, bias=None, gate=None, residual=None, condition=None, raw=False, residual_rows=None,
+                rows_per_sequence=1, valid_rows_per_sequence=0, input_repeat=1, value_scale=1.0, residual_scale=1.0,
+                output_scale=1.0, alpha=0.1, activation=0):
+        bias, _ = _rows2d(bias)
+        gate, gate_rows = _rows2d(gate)
+        residual, res_rows = _rows2d(residual)
+        condition, condition_rows = _rows2d(condition)
+        raw_out = np.zeros((rows, cols), dtype=np.uint16) if raw else None
+        index = np.ascontiguousarray(residual_rows, dtype=np.int32) if residual_rows is not None else None
+        keep.extend([bias, gate, residual, condition, raw_out, index])
+        return OracleFinish(_ptr(bias), _ptr(gate), _ptr(residual), _ptr(condition), _ptr(raw_out), _ptr(index), gate_rows,
+                            res_rows, condition_rows, rows_per_sequence, valid_rows_per_sequence, input_repeat, value_scale,
+                            residual_scale, output_scale, alpha, activation), raw_out
+
+    @staticmethod
+    def _norm(keep, weight, bias, eps, residual=None, projection_bias=None, gate=None, shift=None, scale=None,
+              rows_per_sequence=1, source_rows=None):
+        weight, _ = _rows2d(weight)
+        bias, _ = _rows2d(bias)
+        projection_bias, _ = _rows2d(projection_bias)
+        residual, residual_rows = _rows2d(residual)
+        gate, gate_rows = _rows2d(gate)
+        scale, scale_rows = _rows2d(scale)
+        shift, shift_rows = _rows2d(shift)
+        index = np.ascontiguousarray(source_rows, dtype=np.int32) if source_rows is not None else None
+        keep.extend([weight, bias, projection_bias, residual, gate, scale, shift, index])
+        return OracleNorm(_ptr(weight), _ptr(bias), _ptr(projection_bias), _ptr(residual), _ptr(gate), _ptr(scale), _ptr(shift),
+                          residual_rows, gate_rows, scale_rows, shift_rows, rows_per_sequence, _ptr(index), eps)
+
+    def pointwise(self, x16, type_=BF16, **finish):
+        """-> (y, raw or None); output rows = input rows * input_repeat."""
+        x16 = np.ascontiguousarray(x16, dtype=np.uint16)
+        rows, cols = x16.shape[0] * finish.get("input_repeat", 1), x16.shape[1]
+        keep = []
+        f, raw = self._finish(rows, cols, keep, **finish)
+        y = np.zeros((rows, cols), dtype=np.uint16)
+        self.lib.oracle_pointwise(_ptr(x16), x16.shape[0], rows, cols, type_, C.byref(f), _ptr(y))
+        return y, raw
+
+    def pointwise_quantize(self, x16, fmt, group=0, rotation=0, type_=BF16, **finish):
+        """-> (retained, raw or None, values, scales)."""
+        x16 = np.ascontiguousarray(x16, dtype=np.uint16)
+        rows, cols = x16.shape[0] * finish.get("input_repeat", 1), x16.shape[1]
+        keep = []
+        f, raw = self._finish(rows, cols, keep, **finish)
+        retained = np.zeros((rows, cols), dtype=np.uint16)
+        values = np.zeros((rows, cols), dtype=np.uint8)
+        scales = np.zeros(((cols + group - 1) // group, rows) if group else (rows,), dtype=np.float32)
+        self.lib.oracle_pointwise_quantize(_ptr(x16), x16.shape[0], rows, cols, type_, C.byref(f), _ptr(retained), _ptr(values),
+                                           _ptr(scales), fmt, group, rotation)
+        return retained, raw, values, scales
+
+    def layer_norm_quantize(self, x16, weight16, bias16, eps, fmt, group=0, rotation=0, type_=BF16, **fusion):
+        """-> (normalized, raw, values, scales)."""
+        x16 = np.ascontiguousarray(x16, dtype=np.uint16)
+        source = fusion.get("source_rows")
+        rows, cols = (len(source) if source is not None else x16.shape[0]), x16.shape[1]
+        keep = []
+        n = self._norm(keep, weight16, bias16, eps, **fusion)
+        normalized, raw = np.zeros((rows, cols), dtype=np.uint16), np.zeros((rows, cols), dtype=np.uint16)
+        values = np.zeros((rows, cols), dtype=np.uint8)
+        scales = np.zeros(((cols + group - 1) // group, rows) if group else (rows,), dtype=np.float32)
+        self.lib.oracle_layer_norm_quantize(_ptr(x16), x16.shape[0], rows, cols, type_, C.byref(n), _ptr(normalized), _ptr(raw),
+                                            _ptr(values), _ptr(scales), fmt, group, rotation)
+        return normalized, raw, values, scales
+
+    def normalized_linear(self, x16, weight16, bias16, eps, wq, sw, fmt, type_=BF16, fusion=None, **finish):
+        """-> (out, encoded, encoded_scales, normalized, raw)."""
+        x16 = np.ascontiguousarray(x16, dtype=np.uint16)
+        rows, cols = x16.shape
+        channels = wq.shape[0]
+        keep = []
+        n = self._norm(keep, weight16, bias16, eps, **(fusion or {}))
+        f, _ = self._finish(rows, channels, keep, **finish)
+        out = np.zeros((rows, channels), dtype=np.uint16)
+        encoded, scales = np.zeros((rows, cols), dtype=np.uint8), np.zeros(rows, dtype=np.float32)
+        normalized, raw = np.zeros((rows, cols), dtype=np.uint16), np.zeros((rows, cols), dtype=np.uint16)
+        wq, sw = np.ascontiguousarray(wq, dtype=np.uint8), np.ascontiguousarray(sw, dtype=np.float32)
+        self.lib.oracle_normalized_linear(_ptr(x16), rows, cols, type_, C.byref(n), _ptr(wq), _ptr(sw), channels, fmt, C.byref(f),
+                                          _ptr(out), _ptr(encoded), _ptr(scales), _ptr(normalized), _ptr(raw))
+        return out, encoded, scales, normalized, raw
 
 
 def build_oracle():

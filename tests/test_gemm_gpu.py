@@ -139,6 +139,37 @@ def test_fused_epilogue_chain(oracle, ctx_factory):
     assert np.array_equal(bf16_bits(out), want)
 
 
+def test_fused_epilogue_chain_with_rounding_scales(oracle, reference_kernels, ctx_factory):
+    """Value, residual and output scales that are not powers of two: the reference's finishing pass contracts
+    value_scale*v + residual_scale*skip into one product and a fused multiply-add; the GEMM's fused chain, the
+    oracle and the reference's GEMM followed by its finishing pass must all give the same bf16 bits."""
+    import ctypes as C
+    from tests.oracle_binding import ref_epilogue, ref_view
+    ctx = ctx_factory("int8")
+    m, n, k = 64, 768, 1024
+    (xq, sx, wq, sw), (xv, wv) = make_operands(oracle, m, n, k, I8, 0, 0, seed=17)
+    bias16 = oracle.to_bf16(synth.weights(1, n, 5, std=0.5))
+    res16 = oracle.to_bf16(synth.activations(m, n, 6, outlier_columns=0))
+    scales = dict(value_scale=0.7, residual_scale=1.3, output_scale=0.9)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    ctx.quant_linear((TCGEN05, 64, 128, 2), xv, wv, out, bias=bf16_tensor(bias16), residual=bf16_tensor(res16), activation=1,
+                     **scales)
+    want, _ = oracle.quant_linear(xq, sx, wq, sw, I8, bias=bias16.ravel(), residual=res16, activation=1, **scales)
+    assert ctx.status() == 0 and np.array_equal(bf16_bits(out), want)
+    plain = torch.empty_like(out)
+    workspace = torch.zeros(8 << 20, dtype=torch.uint8, device="cuda")
+    rc = reference_kernels.ttsref_quant_linear(2, 16, 64, 1, m, n, k, 0, 0, xv.values.data_ptr(), xv.scales.data_ptr(),
+                                               wv.values.data_ptr(), wv.scales.data_ptr(), plain.data_ptr(),
+                                               workspace.data_ptr(), workspace.numel(), None, I8, BF16)
+    assert rc == 0, reference_kernels.ttsref_last_error()
+    theirs = torch.empty_like(out)
+    ep = ref_epilogue(bias=bf16_tensor(bias16), residual=bf16_tensor(res16), activation=1, **scales)
+    rc = reference_kernels.ttsref_pointwise(C.byref(ref_view(plain)), C.byref(ref_view(theirs)), BF16, C.byref(ep), None)
+    assert rc == 0, reference_kernels.ttsref_last_error()
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), theirs.view(torch.int16))
+
+
 @pytest.mark.parametrize("activation", [1, 2, 3, 4, 5, 7, 8])  # relu, leaky relu, silu, gelu, gelu-tanh, tanh, sigmoid
 @pytest.mark.parametrize("m,tokens,splits", [(16, 16, 2), (100, 128, 1)])
 def test_fused_activations(oracle, ctx_factory, activation, m, tokens, splits):

@@ -264,3 +264,63 @@ def test_oracle_producers_against_reference_held_fixtures(oracle):
                 a, b = decode[mine_q], decode[theirs_q]
                 close = np.abs(a - b) <= 0.13 * np.maximum(np.abs(a), np.abs(b)) + 2.0 ** -9  # one e4m3 step
                 assert close.mean() > 0.999 and (mine_q != theirs_q).mean() < 0.05, case
+
+
+def test_finish_chain_known_answers(oracle):
+    # reference: Finish::apply, src/ops/kernels/sequence/sequence_internal.cuh:52-74
+    x = oracle.to_bf16(np.array([[30.0, -2.0, 1.0, 1.0]], dtype=np.float32))
+    bias = oracle.to_bf16(np.array([[0.0078125, 0.5, 0.0, 0.0]], dtype=np.float32))  # 2^-7 vanishes next to 30 in bf16
+    y, raw = oracle.pointwise(x, bias=bias, activation=1, raw=True)
+    assert oracle.from_bf16(y).tolist() == [[30.0, 0.0, 1.0, 1.0]]
+    assert oracle.from_bf16(raw).tolist() == [[30.0, -1.5, 1.0, 1.0]]      # raw holds the value before the activation
+    # a residual row index past the end poisons the row, -1 adds nothing (sequence_internal.cuh:63-66)
+    res = oracle.to_bf16(np.ones((2, 4), dtype=np.float32))
+    y, _ = oracle.pointwise(np.repeat(x, 3, axis=0), residual=res, residual_rows=np.array([1, -1, 2]))
+    out = oracle.from_bf16(y)
+    assert out[0].tolist() == [31.0, -1.0, 2.0, 2.0] and out[1].tolist() == [30.0, -2.0, 1.0, 1.0] and np.isnan(out[2]).all()
+    # rows past valid_rows_per_sequence are zeroed, the gate is per sequence, input rows repeat
+    gate = oracle.to_bf16(np.array([[2.0] * 4, [0.5] * 4], dtype=np.float32))
+    y, _ = oracle.pointwise(x, gate=gate, rows_per_sequence=2, valid_rows_per_sequence=1, input_repeat=4)
+    out = oracle.from_bf16(y)
+    assert out[0].tolist() == [60.0, -4.0, 2.0, 2.0] and not out[1].any() and out[2].tolist() == [15.0, -1.0, 0.5, 0.5]
+    # value_scale * v + residual_scale * skip is one rounded product and a fused multiply-add (the reference's
+    # finishing pass is built with contraction): 0.7f*3 + fl(1.3f*7) differs from fl(0.7f*3) + fl(1.3f*7) in fp32
+    v, r = np.float32(-0.9296875), np.float32(1.53125)
+    one = oracle.to_bf16(np.array([[v]], dtype=np.float32))
+    y, _ = oracle.pointwise(one, residual=oracle.to_bf16(np.array([[r]], dtype=np.float32)), value_scale=0.7, residual_scale=1.3)
+    assert float(oracle.from_bf16(y)[0, 0]) == 1.3359375  # separate roundings would give 1.34375
+
+
+def test_oracle_sequence_operators_against_reference_held_fixtures(oracle):
+    """Finishing pass, finish + quantize, LayerNorm + quantize and the fused norm + quantize + projection: the oracle's
+    answers are frozen in the fixtures and compared with what the REFERENCE's kernels produced on the same inputs (`ref_*`,
+    recorded on a B200). The finishing chain (ReLU, scales that are not powers of two) is exact arithmetic: bit for bit.
+    LayerNorm goes through the GPU's approximate rsqrt: normalized values within one bf16 step, bytes within one
+    quantization step, projection outputs within 2e-2 relative (floor 1e-2 * rms)."""
+    from tests.golden.make_golden import sequence_oracle
+    index = json.loads((GOLDEN / "index.json").read_text())
+    assert index.get("sequence"), "no sequence fixtures"
+    decode = np.array([oracle.lib.oracle_fp8_e4m3_decode(v) for v in range(256)], dtype=np.float64)
+    for case in index["sequence"]:
+        data = np.load(GOLDEN / case["file"])
+        fmt, group, rotation = case["format"], case["group"], case["rotation"]
+        mine = sequence_oracle(oracle, data, fmt, group, rotation)
+        for key, value in mine.items():  # the oracle has not drifted from what was frozen
+            assert np.array_equal(np.asarray(value).view(np.uint8), data[key].view(np.uint8)), (case, key)
+        for key in ("pw_y", "pw_raw", "pwq_retained", "pwq_values", "ln_raw"):
+            assert np.array_equal(mine[key], data["ref_" + key]), (case, key)
+        assert np.array_equal(mine["pwq_scales"].ravel().view(np.uint32), data["ref_pwq_scales"].ravel().view(np.uint32)), case
+        a, b = _bf16(mine["ln_normalized"]), _bf16(data["ref_ln_normalized"])
+        assert np.all(np.abs(a - b) <= 2.0 ** -7 * np.maximum(np.abs(a), np.abs(b))), case
+        assert np.allclose(mine["ln_scales"].ravel(), data["ref_ln_scales"].ravel(), rtol=2e-2), case
+        if fmt == I8:
+            step = np.abs(mine["ln_values"].view(np.int8).astype(np.int32) - data["ref_ln_values"].view(np.int8).astype(np.int32))
+            assert step.max() <= 1 + (1 if rotation else 0), (case, step.max())
+        else:
+            qa, qb = decode[mine["ln_values"]], decode[data["ref_ln_values"]]
+            close = np.abs(qa - qb) <= 0.13 * np.maximum(np.abs(qa), np.abs(qb)) + 2.0 ** -9
+            assert close.mean() > 0.999, case
+        if not group:
+            want, got = _bf16(mine["nl_out"]), _bf16(data["ref_nl_out"])
+            floor = 1e-2 * np.sqrt(np.mean(want ** 2))
+            assert np.max(np.abs(got - want) / np.maximum(np.abs(want), floor)) < 2e-2, case

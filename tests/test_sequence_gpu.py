@@ -69,12 +69,15 @@ def epilogue_case(rows, cols, dtype, seed, activation, what):
         kw.update(rows_per_sequence=rows // sequences, valid_rows_per_sequence=max(1, rows // sequences - 1))
     if "scale" in what:
         kw["output_scale"] = 0.25
+    if "odd" in what:  # scales whose products round: a fused multiply-add anywhere in the chain would show
+        kw.update(value_scale=0.7, residual_scale=1.3, output_scale=0.9)
     return kw
 
 
 POINTWISE = [(16, 512, 0, "bias"), (64, 2048, 1, "bias gate residual raw"), (12, 776, 2, "bias condition mask raw scale"),
              (20, 4096, 1, "indexed gate"), (8, 100, 0, "bias residual"), (32, 1024, 6, "bias gate"), (32, 1024, 3, "bias scale"),
-             (16, 640, 4, "residual"), (16, 640, 5, "bias"), (16, 640, 7, "condition"), (16, 640, 8, "bias raw")]
+             (16, 640, 4, "residual"), (16, 640, 5, "bias"), (16, 640, 7, "condition"), (16, 640, 8, "bias raw"),
+             (64, 2048, 0, "bias residual odd"), (24, 1000, 1, "bias gate residual raw odd"), (20, 512, 2, "indexed odd")]
 
 
 @pytest.mark.parametrize("type_code", [BF16, F16])
@@ -123,7 +126,8 @@ QUANTIZE = [(16, 512, I8, 0, 0), (64, 2048, I8, 0, 0), (7, 3000, FP8, 0, 0), (64
 
 @pytest.mark.parametrize("type_code", [BF16, F16])
 @pytest.mark.parametrize("rows,cols,fmt,group,rotation", QUANTIZE)
-@pytest.mark.parametrize("activation,what", [(1, "bias gate residual raw"), (0, "bias mask scale"), (3, "bias")])
+@pytest.mark.parametrize("activation,what", [(1, "bias gate residual raw"), (0, "bias mask scale"), (3, "bias"),
+                                             (0, "bias residual odd")])
 def test_finish_and_quantize_matches_reference(reference_kernels, ctx_factory, type_code, rows, cols, fmt, group, rotation,
                                                activation, what):
     dtype = DTYPES[type_code]
@@ -314,3 +318,145 @@ def test_linear_with_an_epilogue_the_gemm_cannot_fuse(reference_kernels, ctx_fac
         torch.cuda.synchronize()
         assert steps_apart(out, finished, dtype) <= 2
     assert torch.equal(bits(raw), bits(raw_theirs))
+
+
+# ---------------------------------------------------------------------------------------------------------
+# The same operators against the CPU oracle (oracle/oracle.cpp restates Finish::apply, the finish-and-
+# quantize pass, LayerNorm + quantize and the fused norm + quantize + projection in scalar loops).
+# Bars: exact arithmetic chains bit for bit; LayerNorm within one storage step / one quantization step (the
+# device's rsqrtf is approximate, the oracle's 1/sqrt is not); transcendental activations within two steps.
+def host16(t):
+    return None if t is None else t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def host_kwargs(kw):
+    out = {}
+    for key, value in kw.items():
+        if torch.is_tensor(value):
+            out[key] = value.cpu().numpy().astype(np.int32) if value.dtype == torch.int32 else host16(value)
+        else:
+            out[key] = value
+    return out
+
+
+def from16(bits16, dtype):
+    return torch.from_numpy(bits16.view(np.int16)).view(dtype).double()
+
+
+def decoded(values, fmt, oracle):
+    raw = values.cpu().numpy() if torch.is_tensor(values) else values
+    if fmt == I8:
+        return raw.view(np.int8).astype(np.float64)
+    table = np.array([oracle.lib.oracle_fp8_e4m3_decode(q) for q in range(256)], dtype=np.float64)
+    return table[raw]
+
+
+def assert_within_one_quantization_step(oracle, fmt, group, mine, want_values, want_scales):
+    """Dequantized rows agree to one step of the format at that magnitude (plus one storage step of the scale)."""
+    rows, cols = want_values.shape
+    def expand(scales):
+        s = scales.cpu().numpy() if torch.is_tensor(scales) else scales
+        return np.repeat(s.reshape(-1, rows).T, group, axis=1)[:, :cols] if group else s.reshape(rows, 1) * np.ones((1, cols))
+    a, b = decoded(mine.values, fmt, oracle), decoded(want_values, fmt, oracle)
+    sa, sb = expand(mine.scales).astype(np.float64), expand(want_scales).astype(np.float64)
+    step = np.maximum(sa, sb) * (1.0 if fmt == I8 else np.maximum(np.maximum(np.abs(a), np.abs(b)) * 2.0 ** -3, 2.0 ** -9))
+    assert np.all(np.abs(a * sa - b * sb) <= 1.01 * step + np.abs(b * sb) * 2.0 ** -7)
+
+
+@pytest.mark.parametrize("type_code", [BF16, F16])
+@pytest.mark.parametrize("rows,cols,activation,what", POINTWISE)
+def test_finishing_pass_matches_oracle(oracle, ctx_factory, type_code, rows, cols, activation, what):
+    dtype = DTYPES[type_code]
+    ctx = ctx_factory("int8")
+    x = randn(rows, cols, 10 * rows + cols, dtype)
+    kw = epilogue_case(rows, cols, dtype, rows + cols, activation, what)
+    mine = torch.empty_like(x)
+    raw_mine = torch.zeros_like(x) if "raw" in what else None
+    ctx.pointwise(x, mine, raw=raw_mine, **kw)
+    torch.cuda.synchronize()
+    want, want_raw = oracle.pointwise(host16(x), type_code, raw="raw" in what, **host_kwargs(kw))
+    if raw_mine is not None:
+        assert np.array_equal(host16(raw_mine), want_raw)
+    if activation in (0, 1, 2):
+        assert np.array_equal(host16(mine), want)
+    else:
+        # libm on the host, device intrinsics (and the hardware's approximate tanh) on the GPU: two storage steps, or
+        # 2e-3 absolute where the activation's value is tiny next to its argument
+        got, expect = mine.double().cpu(), from16(want, dtype)
+        mantissa = 8 if dtype == torch.bfloat16 else 11
+        spacing = torch.maximum(got.abs(), expect.abs()).clamp_min(1e-30).log2().floor().exp2() * 2.0 ** (1 - mantissa)
+        assert bool(((got - expect).abs() <= 2 * spacing + 2e-3).all())
+
+
+@pytest.mark.parametrize("type_code", [BF16, F16])
+@pytest.mark.parametrize("rows,cols,fmt,group,rotation", [(16, 512, I8, 0, 0), (7, 3000, FP8, 0, 0), (5, 9000, I8, 0, 0),
+                                                          (16, 2048, I8, 128, 128), (12, 768, FP8, 32, 0), (9, 1024, FP8, 128, 128)])
+@pytest.mark.parametrize("activation,what", [(1, "bias gate residual raw"), (0, "bias mask scale"), (2, "bias residual odd")])
+def test_finish_and_quantize_matches_oracle(oracle, ctx_factory, type_code, rows, cols, fmt, group, rotation, activation, what):
+    dtype = DTYPES[type_code]
+    ctx = ctx_factory(ctx_mode(fmt, group))
+    x = randn(rows, cols, rows + cols + fmt, dtype, 2.0)
+    kw = epilogue_case(rows, cols, dtype, rows * 3 + cols, activation, what)
+    mine = quantized(rows, cols, fmt, group, rotation)
+    kept, raw_mine = torch.zeros_like(x), (torch.zeros_like(x) if "raw" in what else None)
+    ctx.pointwise_quantize(x, mine, retained=kept, raw=raw_mine, **kw)
+    torch.cuda.synchronize()
+    want_kept, want_raw, values, scales = oracle.pointwise_quantize(host16(x), fmt, group, rotation, type_code, raw="raw" in what,
+                                                                    **host_kwargs(kw))
+    if raw_mine is not None:
+        assert np.array_equal(host16(raw_mine), want_raw)
+    assert np.array_equal(host16(kept), want_kept)
+    assert np.array_equal(mine.scales.cpu().numpy().reshape(scales.shape).view(np.uint32), scales.view(np.uint32))
+    assert np.array_equal(mine.values.cpu().numpy(), values)
+
+
+@pytest.mark.parametrize("type_code", [BF16, F16])
+@pytest.mark.parametrize("rows,cols,fmt,group,rotation,what", [case for case in NORM if "gather" not in case[5]])
+def test_layer_norm_quantize_matches_oracle(oracle, ctx_factory, type_code, rows, cols, fmt, group, rotation, what):
+    dtype = DTYPES[type_code]
+    ctx = ctx_factory(ctx_mode(fmt, group))
+    x = randn(rows, cols, rows + cols, dtype, 1.5) + 0.25
+    weight = randn(1, cols, 2, dtype, 0.2) + 1 if "weight" in what else None
+    bias = randn(1, cols, 3, dtype, 0.3) if "bias" in what else None
+    sequences = rows // 4 if rows % 4 == 0 else 1
+    fusion = {}
+    if "residual" in what:
+        fusion["residual"] = randn(rows, cols, 4, dtype)
+    if "projection" in what:
+        fusion["projection_bias"] = randn(1, cols, 5, dtype, 0.5)
+    for i, name in enumerate(("gate", "shift", "scale")):
+        if name in what:
+            fusion[name] = randn(sequences, cols, 6 + i, dtype, 0.5)
+            fusion["rows_per_sequence"] = rows // sequences
+    mine = quantized(rows, cols, fmt, group, rotation)
+    kept, raw_mine = torch.zeros_like(x), torch.zeros_like(x)
+    ctx.layer_norm_quantize(x, mine, weight, bias, 1e-5, retained=kept, raw=raw_mine, **fusion)
+    torch.cuda.synchronize()
+    normalized, raw, values, scales = oracle.layer_norm_quantize(host16(x), host16(weight), host16(bias), 1e-5, fmt, group,
+                                                                 rotation, type_code, **host_kwargs(fusion))
+    assert np.array_equal(host16(raw_mine), raw)            # the value that is normalized: exact arithmetic
+    assert steps_apart(kept.cpu(), from16(normalized, dtype), dtype) <= 1
+    if not rotation:
+        assert_within_one_quantization_step(oracle, fmt, group, mine, values, scales)
+
+
+@pytest.mark.parametrize("type_code", [BF16, F16])
+@pytest.mark.parametrize("rows,k,n,fmt", [(16, 512, 256, I8), (5, 384, 100, I8), (16, 512, 192, FP8), (33, 128, 72, FP8)])
+def test_fused_norm_projection_matches_oracle(oracle, ctx_factory, type_code, rows, k, n, fmt):
+    from breeze_tts_cpp_b200 import ops
+    dtype = DTYPES[type_code]
+    ctx = ctx_factory(ctx_mode(fmt, 0))
+    x = randn(rows, k, rows + k + n, dtype, 1.5)
+    wv = ctx.quantize_rows(randn(n, k, 3, dtype, 0.05), ops.RowScaledView.empty(n, k, fmt))
+    norm_weight, norm_bias = randn(1, k, 4, dtype, 0.2) + 1, randn(1, k, 5, dtype, 0.3)
+    residual, out_bias = randn(rows, k, 6, dtype), randn(1, n, 7, dtype, 0.5)
+    mine = torch.empty(rows, n, dtype=dtype, device="cuda")
+    assert ctx.normalized_linear(x, wv, mine, norm_weight, norm_bias, 1e-5, bias=out_bias, fusion=dict(residual=residual),
+                                 activation=1)
+    torch.cuda.synchronize()
+    want, *_ = oracle.normalized_linear(host16(x), host16(norm_weight), host16(norm_bias), 1e-5, wv.values.cpu().numpy(),
+                                        wv.scales.cpu().numpy().ravel(), fmt, type_code, fusion=dict(residual=host16(residual)),
+                                        bias=host16(out_bias), activation=1)
+    got, expect = mine.double().cpu().numpy(), from16(want, dtype).numpy()
+    floor = 1e-2 * np.sqrt(np.mean(expect ** 2)) + 1e-30
+    assert float(np.max(np.abs(got - expect) / np.maximum(np.abs(expect), floor))) < 2e-2
