@@ -31,6 +31,7 @@
 #pragma once
 #include "kernels/sm100_ptx.cuh"
 #include "kernels/quant_linear_geometry.h"
+#include "kernels/sequence_finish.cuh"
 #include "core/tensor.h"
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -81,22 +82,9 @@ __device__ __forceinline__ float load_as(const void *p, size_t i, int type) {
     return type == int(Type::F16) ? __half2float(static_cast<const __half *>(p)[i])
                                   : __bfloat162float(static_cast<const __nv_bfloat16 *>(p)[i]);
 }
-// reference: src/ops/kernels/common/activation.cuh:5-27
-__device__ __forceinline__ float activate(float x, int kind, float alpha) {
-    switch (kind) {
-    case 1: return fmaxf(x, 0.f);
-    case 2: return x >= 0 ? x : x * alpha;
-    case 3: return x / (1.f + expf(-x));
-    case 4: return .5f * x * (1.f + erff(x * .7071067811865475f));
-    case 5: return .5f * x * (1.f + tanhf(.7978845608028654f * (x + .044715f * x * x * x)));
-    case 7: return tanhf(x);
-    case 8: return 1.f / (1.f + expf(-x));
-    default: return x;
-    }
-}
-
 // Post-GEMM chain on one rounded value; rounding points follow the reference's separate pass
-// (src/ops/kernels/sequence/sequence_internal.cuh:52-74). `bias` and `skip` are already fp32
+// (src/ops/kernels/sequence/sequence_internal.cuh:52-74; the activations are the finishing pass's own
+// instruction sequences, so GEMM + fused chain equals GEMM followed by that pass bit for bit). `bias` and `skip` are already fp32
 // (0 when absent). Deliberately not inlined: the transcendental activations are large, and eight
 // inlined copies per row pushed the common no-chain path out of the instruction cache.
 __device__ __noinline__ float finish_chain(const FusedEpilogue &e, int type, float value, float bias, float skip) {
@@ -105,7 +93,7 @@ __device__ __noinline__ float finish_chain(const FusedEpilogue &e, int type, flo
     if (e.residual || e.value_scale != 1.f)
         value = round_to(__fmaf_rn(e.value_scale, value, __fmul_rn(e.residual_scale, skip)), type); // contracted as in the reference's finishing pass
     if (e.activation || e.output_scale != 1.f)
-        value = activate(round_to(__fmul_rn(value, e.output_scale), type), e.activation, e.alpha);
+        value = finish_activation(round_to(__fmul_rn(value, e.output_scale), type), e.activation, e.alpha);
     return value;
 }
 __device__ __forceinline__ uint32_t pack16(float lo, float hi, int type) {

@@ -139,10 +139,12 @@ def test_fused_epilogue_chain(oracle, ctx_factory):
     assert np.array_equal(bf16_bits(out), want)
 
 
-def test_fused_epilogue_chain_with_rounding_scales(oracle, reference_kernels, ctx_factory):
+@pytest.mark.parametrize("activation", [0, 1, 2, 3, 4, 5, 7, 8])
+def test_fused_epilogue_chain_with_rounding_scales(oracle, reference_kernels, ctx_factory, activation):
     """Value, residual and output scales that are not powers of two: the reference's finishing pass contracts
-    value_scale*v + residual_scale*skip into one product and a fused multiply-add; the GEMM's fused chain, the
-    oracle and the reference's GEMM followed by its finishing pass must all give the same bf16 bits."""
+    value_scale*v + residual_scale*skip into one product and a fused multiply-add. The GEMM's fused chain and the
+    reference's GEMM followed by its finishing pass must give the same bf16 bits for every activation the chain
+    fuses; the oracle (libm activations) too where the activation is exact arithmetic."""
     import ctypes as C
     from tests.oracle_binding import ref_epilogue, ref_view
     ctx = ctx_factory("int8")
@@ -152,10 +154,13 @@ def test_fused_epilogue_chain_with_rounding_scales(oracle, reference_kernels, ct
     res16 = oracle.to_bf16(synth.activations(m, n, 6, outlier_columns=0))
     scales = dict(value_scale=0.7, residual_scale=1.3, output_scale=0.9)
     out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
-    ctx.quant_linear((TCGEN05, 64, 128, 2), xv, wv, out, bias=bf16_tensor(bias16), residual=bf16_tensor(res16), activation=1,
-                     **scales)
-    want, _ = oracle.quant_linear(xq, sx, wq, sw, I8, bias=bias16.ravel(), residual=res16, activation=1, **scales)
-    assert ctx.status() == 0 and np.array_equal(bf16_bits(out), want)
+    ctx.quant_linear((TCGEN05, 64, 128, 2), xv, wv, out, bias=bf16_tensor(bias16), residual=bf16_tensor(res16),
+                     activation=activation, alpha=0.2, **scales)
+    assert ctx.status() == 0
+    if activation in (0, 1, 2):
+        want, _ = oracle.quant_linear(xq, sx, wq, sw, I8, bias=bias16.ravel(), residual=res16, activation=activation, alpha=0.2,
+                                      **scales)
+        assert np.array_equal(bf16_bits(out), want)
     plain = torch.empty_like(out)
     workspace = torch.zeros(8 << 20, dtype=torch.uint8, device="cuda")
     rc = reference_kernels.ttsref_quant_linear(2, 16, 64, 1, m, n, k, 0, 0, xv.values.data_ptr(), xv.scales.data_ptr(),
@@ -163,7 +168,7 @@ def test_fused_epilogue_chain_with_rounding_scales(oracle, reference_kernels, ct
                                                workspace.data_ptr(), workspace.numel(), None, I8, BF16)
     assert rc == 0, reference_kernels.ttsref_last_error()
     theirs = torch.empty_like(out)
-    ep = ref_epilogue(bias=bf16_tensor(bias16), residual=bf16_tensor(res16), activation=1, **scales)
+    ep = ref_epilogue(bias=bf16_tensor(bias16), residual=bf16_tensor(res16), activation=activation, alpha=0.2, **scales)
     rc = reference_kernels.ttsref_pointwise(C.byref(ref_view(plain)), C.byref(ref_view(theirs)), BF16, C.byref(ep), None)
     assert rc == 0, reference_kernels.ttsref_last_error()
     torch.cuda.synchronize()

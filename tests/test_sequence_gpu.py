@@ -3,10 +3,9 @@ quantize, LayerNorm + quantize, and the fused norm + quantize + projection — a
 own kernels on identical inputs (src/ops/kernels/sequence/sequence_pointwise.cu,
 sequence_norm.cu, built into oracle/_ref).
 
-Bars: bytes, scales and every 16-bit side output identical wherever the chain is exact arithmetic
-(identity / ReLU / leaky ReLU, power-of-two epilogue scales); with a transcendental activation the
-16-bit outputs agree within two steps of the storage type and the quantized bytes within one step
-(the device's expf / erff / tanhf are evaluated by different instruction sequences in the two builds).
+Bar: bytes, scales and every 16-bit side output identical to the reference kernels' for every activation
+(the transcendental ones are evaluated by the same device instruction sequences in both builds) and for
+epilogue scales that are not powers of two (the reference build contracts its scale-and-add).
 """
 import ctypes as C
 
@@ -77,7 +76,9 @@ def epilogue_case(rows, cols, dtype, seed, activation, what):
 POINTWISE = [(16, 512, 0, "bias"), (64, 2048, 1, "bias gate residual raw"), (12, 776, 2, "bias condition mask raw scale"),
              (20, 4096, 1, "indexed gate"), (8, 100, 0, "bias residual"), (32, 1024, 6, "bias gate"), (32, 1024, 3, "bias scale"),
              (16, 640, 4, "residual"), (16, 640, 5, "bias"), (16, 640, 7, "condition"), (16, 640, 8, "bias raw"),
-             (64, 2048, 0, "bias residual odd"), (24, 1000, 1, "bias gate residual raw odd"), (20, 512, 2, "indexed odd")]
+             (64, 2048, 0, "bias residual odd"), (24, 1000, 1, "bias gate residual raw odd"), (20, 512, 2, "indexed odd"),
+             (64, 4096, 3, "bias odd"), (64, 4096, 4, "bias odd"), (64, 4096, 5, "bias residual odd"), (64, 4096, 6, "bias odd"),
+             (64, 4096, 7, "bias odd"), (64, 4096, 8, "bias residual odd")]
 
 
 @pytest.mark.parametrize("type_code", [BF16, F16])
@@ -97,10 +98,7 @@ def test_finishing_pass_matches_reference(reference_kernels, ctx_factory, type_c
     torch.cuda.synchronize()
     if raw_mine is not None:
         assert torch.equal(bits(raw_mine), bits(raw_theirs))
-    if activation in (0, 1, 2):
-        assert torch.equal(bits(mine), bits(theirs))
-    else:
-        assert steps_apart(mine, theirs, dtype) <= 2
+    assert torch.equal(bits(mine), bits(theirs))
     # in place
     again = x.clone()
     ctx.pointwise(again, again, raw=raw_mine, **kw)
@@ -147,13 +145,9 @@ def test_finish_and_quantize_matches_reference(reference_kernels, ctx_factory, t
     torch.cuda.synchronize()
     if raw_mine is not None:
         assert torch.equal(bits(raw_mine), bits(raw_theirs))
-    if activation in (0, 1, 2):
-        assert torch.equal(bits(kept_mine), bits(kept_theirs))
-        assert torch.equal(mine.scales.view(torch.int32), theirs.scales.view(torch.int32))
-        assert torch.equal(mine.values, theirs.values)
-    else:
-        assert steps_apart(kept_mine, kept_theirs, dtype) <= 2
-        assert float((mine.scales / theirs.scales - 1).abs().max()) < 2e-2
+    assert torch.equal(bits(kept_mine), bits(kept_theirs))
+    assert torch.equal(mine.scales.view(torch.int32), theirs.scales.view(torch.int32))
+    assert torch.equal(mine.values, theirs.values)
 
 
 def test_finish_and_quantize_rejects_bad_requests(ctx_factory):
