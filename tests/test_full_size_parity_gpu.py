@@ -218,12 +218,16 @@ def test_k_group_down_projection_m4096(oracle, reference_kernels, ctx_factory, m
     channels = channel_slice(n, 128, seed=3)
     rows = np.unique(np.concatenate([np.arange(0, m, 128), np.arange(127, m, 128),
                                      np.random.default_rng(1).integers(0, m, 64)]))
-    _, exact = oracle_slice(oracle, xv, wv, fmt, 128, channels, rows=rows, residual=skip)
-    got = out[torch.from_numpy(rows).cuda()][:, torch.from_numpy(channels).cuda()].float().cpu().numpy()
-    assert rel_err(got, exact) < tol
+    want16, exact = oracle_slice(oracle, xv, wv, fmt, 128, channels, rows=rows, residual=skip)
+    picked = out[torch.from_numpy(rows).cuda()][:, torch.from_numpy(channels).cuda()]
+    assert rel_err(picked.float().cpu().numpy(), exact) < tol
+    if fmt == I8:  # exact integer partials, one fused multiply-add per K group in K order: the same bits everywhere
+        assert np.array_equal(picked.contiguous().view(torch.int16).cpu().numpy().view(np.uint16), want16)
     if not residual:
         theirs = reference_gemm(reference_kernels, (GROUPED, 64, 64, 1), xv, wv, m, n, k, fmt, group=128)
         assert rel_err(out.float().cpu().numpy(), theirs.float().cpu().numpy()) < tol
+        if fmt == I8:
+            assert torch.equal(out.view(torch.int16), theirs.view(torch.int16))
 
 
 # ------------------------------------------------------------------------------------------------ smaller holes

@@ -100,9 +100,11 @@ def test_k_group_gemm(oracle, ctx_factory, mode, fmt, tol, m, n, k, tokens, spli
     (xq, sx, wq, sw), (xv, wv) = make_operands(oracle, m, n, k, fmt, 128, 128, seed=m + k, student_t=3.0)
     out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
     ctx.quant_linear((TCGEN05, tokens, 128, splits), xv, wv, out)
-    _, exact = oracle.quant_linear(xq, sx, wq, sw, fmt, 128, 128)
+    want16, exact = oracle.quant_linear(xq, sx, wq, sw, fmt, 128, 128)
     assert ctx.status() == 0
     assert rel_err(out.float().cpu().numpy(), exact) < tol
+    if fmt == I8 and splits == 1:  # exact integer partials accumulated in K order: bit for bit
+        assert np.array_equal(bf16_bits(out), want16)
 
 
 @pytest.mark.parametrize("mode,fmt,tol", [("group_int8", I8, 1e-2), ("group_fp8", FP8, 2e-2)])
@@ -311,3 +313,5 @@ def test_k_groups_of_32_and_64(oracle, reference_kernels, ctx_factory, fmt, tol,
         assert rc == 0, reference_kernels.ttsref_last_error()
         torch.cuda.synchronize()
         assert rel_err(out.float().cpu().numpy(), theirs.float().cpu().numpy()) < tol
+        if fmt == I8 and splits == 1:  # same accumulation order as the reference's grouped kernel: same bits
+            assert torch.equal(out.view(torch.int16), theirs.view(torch.int16))
