@@ -423,6 +423,72 @@ def library_tensor_peaks(torch, device):
     return out
 
 
+def sustained_tensor_rates(torch, device, stream, seconds=1.5):
+    """The same dense 8-bit GEMM rates held for `seconds` each instead of a burst, with the clocks seen meanwhile: at
+    these rates a B200 runs into its 1000 W power cap and lowers the SM clock, for this library's prefill kernel and
+    for the vendor library alike, so the burst figures of the `configs` rows and of `tensor_peaks` are upper ends."""
+    from breeze_tts_cpp_b200 import ops
+    k, n, m = SHAPES["gate_up"][0], SHAPES["gate_up"][1], 8192
+    out = {"seconds": seconds, "shape": f"gate_up {k}->{n} at M={m} (this library); 8192^3 (vendor library)"}
+
+    def hold(fn, sync, work):
+        fn()
+        sync()
+        with ClockSampler(device.index) as clocks:
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(stream)
+            calls, began = 0, time.time()
+            while time.time() - began < seconds:
+                for _ in range(10):
+                    fn()
+                calls += 10
+                sync()
+            stop.record(stream)
+            stop.synchronize()
+        seen = clocks.summary()
+        return round(work * calls / (start.elapsed_time(stop) * 1e-3) / 1e12, 1), seen
+
+    with torch.cuda.stream(stream):
+        for mode, fmt, key in (("int8", I8, "int8_tops"), ("fp8", FP8, "fp8_tflops")):
+            ctx = ops.Context(mode, device=device.index, stream=stream, workspace_bytes=8 << 20)
+            ws = [ctx.quantize_rows(synth_weight(torch, n, k, SEED + c, device), ops.RowScaledView.empty(n, k, fmt, device=device))
+                  for c in range(4)]
+            xq = ctx.quantize_rows(synth_activations(torch, m, k, SEED, device).to(torch.bfloat16),
+                                   ops.RowScaledView.empty(m, k, fmt, device=device))
+            y = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+            ctx.prepare_quantized(m, n, k)
+            for w in ws:
+                ctx.matmul(xq, w, y)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for w in ws:
+                    ctx.matmul(xq, w, y)
+            rate, seen = hold(graph.replay, stream.synchronize, 2.0 * m * n * k * len(ws))
+            out[key] = rate
+            out[key.split("_")[0] + "_clocks"] = seen
+            ok = ctx.status() == 0
+            ctx.close()
+            if not ok:
+                out[key] = None
+        side = 8192
+        try:
+            a = torch.randint(-100, 100, (side, side), dtype=torch.int8, device=device)
+            b = torch.randint(-100, 100, (side, side), dtype=torch.int8, device=device).t()
+            out["library_int8_tops"], out["library_int8_clocks"] = hold(lambda: torch._int_mm(a, b), stream.synchronize, 2.0 * side ** 3)
+        except Exception as error:  # noqa: BLE001
+            out["library_int8_tops"], out["library_int8_error"] = None, str(error)[:80]
+        try:
+            a = torch.randn(side, side, device=device).to(torch.float8_e4m3fn)
+            b = torch.randn(side, side, device=device).to(torch.float8_e4m3fn).t()
+            one = torch.ones((), device=device)
+            out["library_fp8_tflops"], out["library_fp8_clocks"] = hold(
+                lambda: torch._scaled_mm(a, b, one, one, out_dtype=torch.bfloat16), stream.synchronize, 2.0 * side ** 3)
+        except Exception as error:  # noqa: BLE001
+            out["library_fp8_tflops"], out["library_fp8_error"] = None, str(error)[:80]
+    return out
+
+
 def check_output(torch, fmt, group, xq, wq, out, residual):
     """Plain PyTorch restatement of the arithmetic on a slice of the output (a checker, never the product): INT8
     per-row must match bit for bit (exact INT32 sums, the same fp32 rounding chain), the other modes within
@@ -742,6 +808,7 @@ def main():
                 tensor_peaks = library_tensor_peaks(torch, device)
                 line["tensor_peaks"] = tensor_peaks
                 line["configs"] = config_rows(torch, device, stream, peaks, tensor_peaks)
+                line["tensor_sustained"] = sustained_tensor_rates(torch, device, stream)
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
