@@ -331,6 +331,16 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             sw8[i] = (!Grouped && columns_ok) ? a.sw[n + i] : 1.f;
             bias8[i] = (e.bias && columns_ok) ? load_as(e.bias, n + i, type) : 0.f;
         }
+        // K-group mode: the weights' group scales of this CTA's K range are static too, one entry per
+        // accumulation unit (a unit past the end of K, whose accumulator holds zeros, takes scale 1).
+        const int unit_count = kb_count * units;
+        float *sx_smem = scale_smem, *sw_smem = scale_smem + size_t(unit_count) * BN;
+        if constexpr (Grouped) {
+            for (int i = e_thread; i < unit_count * kBlockChannels; i += kEpilogueThreads) {
+                const int unit = i / kBlockChannels, channel = n0 + i % kBlockChannels, k0 = kb_begin * kBlockK + unit * unit_k;
+                sw_smem[i] = (a.weight_group && channel < a.n && k0 < a.k) ? a.sw[size_t(k0 / a.weight_group) * a.n + channel] : 1.f;
+            }
+        }
         ptx::wait_for_upstream(); // activation scales, residuals and the output buffer belong to upstream
         float first_residual[8];
         {
@@ -388,19 +398,12 @@ w8a8_tcgen05_gemm(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 }
             }
         } else {
-            // Stage this split's group scales once, one entry per accumulation unit: sx_g[unit][token],
-            // sw_g[unit][channel]. Each operand is indexed by its own group width; a unit past the end of K
-            // (its accumulator holds zeros) takes scale 1.
-            const int unit_count = kb_count * units;
-            float *sx_smem = scale_smem, *sw_smem = scale_smem + size_t(unit_count) * BN;
+            // Stage the activations' group scales of this split (the weights' were staged before the wait):
+            // sx_g[unit][token], each operand indexed by its own group width.
             for (int i = e_thread; i < unit_count * BN; i += kEpilogueThreads) {
                 const int unit = i / BN, token = i % BN, k0 = kb_begin * kBlockK + unit * unit_k;
                 sx_smem[i] = (a.input_group && token < valid_tokens && k0 < a.k)
                                  ? a.sx[size_t(k0 / a.input_group) * a.m + m0 + token] : 1.f;
-            }
-            for (int i = e_thread; i < unit_count * kBlockChannels; i += kEpilogueThreads) {
-                const int unit = i / kBlockChannels, channel = n0 + i % kBlockChannels, k0 = kb_begin * kBlockK + unit * unit_k;
-                sw_smem[i] = (a.weight_group && channel < a.n && k0 < a.k) ? a.sw[size_t(k0 / a.weight_group) * a.n + channel] : 1.f;
             }
             asm volatile("bar.sync 1, 256;" ::: "memory");
             float result[kMyChunks * 16];
