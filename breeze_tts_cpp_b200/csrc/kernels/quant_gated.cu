@@ -29,10 +29,11 @@ template <> __device__ __forceinline__ float round16<__nv_bfloat16>(float v) {
 }
 template <> __device__ __forceinline__ float round16<__half>(float v) { return __half2float(__float2half_rn(v)); }
 
-template <Type F, class T, int Kind, int Items, bool Rotate>
-__global__ void __launch_bounds__(kThreads)
+template <Type F, class T, int Kind, int Items, bool Rotate, int Threads = kThreads>
+__global__ void __launch_bounds__(Threads)
 gated_quantize(const T *__restrict__ input, unsigned char *__restrict__ out, float *__restrict__ scales, int rows,
                int cols, int group, int parts, bool aligned) {
+    constexpr int kThreads = Threads; // shadows the file-wide default inside this kernel
     __shared__ float slots[kThreads / 32];
     pdl_launch_dependents();
     pdl_wait_upstream();
@@ -91,6 +92,20 @@ void launch_items(const T *x, unsigned char *q, float *s, int rows, int cols, in
     int parts = 1;
     if (group)
         while (parts < chunks && parts < 8 && int64_t(rows) * parts <= 2 * sms) parts *= 2;
+    // Short batches with one scale per row (decode): the CTA that holds a row is alone on its multiprocessor, and
+    // with 256 threads the activation arithmetic of 6144 columns is three dependent rounds on two warps per
+    // scheduler. One value group per thread on a CTA three or four times as wide hides those latencies.
+    if (!group && aligned && chunks > 1 && chunks <= 4 && rows <= sms) {
+        const int threads = chunks * kThreads;
+#define B200Q_WIDE(N)                                                                                                   \
+    launch_pdl("quantized gated launch", gated_quantize<F, T, Kind, 1, Rotate, N>, dim3(unsigned(rows)), dim3(N), 0, stream, x, \
+               q, s, rows, cols, group, 1, aligned)
+        if (threads == 512) B200Q_WIDE(512);
+        else if (threads == 768) B200Q_WIDE(768);
+        else B200Q_WIDE(1024);
+#undef B200Q_WIDE
+        return;
+    }
     const int items = (chunks + parts - 1) / parts;
     const unsigned grid = unsigned(rows) * unsigned(parts);
 #define B200Q_RUN(I)                                                                                                  \
