@@ -131,10 +131,11 @@ __device__ __forceinline__ float abs_max8(const float (&v)[8]) {
     return m;
 }
 
-// Max over the whole CTA. `slots` must hold one float per warp. Exact, so the order is irrelevant.
+// Max over the whole CTA of a value that is never negative and never NaN (an absolute maximum built with
+// fmaxf). `slots` must hold one float per warp. Exact, so the order is irrelevant; such floats order like their
+// bit patterns, which lets one warp-reduce instruction replace five shuffle rounds.
 template <int Threads> __device__ __forceinline__ float cta_max(float v, float *slots) {
-#pragma unroll
-    for (int d = 16; d; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
+    v = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(v)));
     if (!(threadIdx.x & 31)) slots[threadIdx.x >> 5] = v;
     __syncthreads();
     float r = 0.f;
