@@ -168,7 +168,11 @@ void launch_prefill_pair(const CUtensorMap &map_w, const CUtensorMap &map_x, con
     attribute.val.programmaticStreamSerializationAllowed = 1;
     config.attrs = &attribute;
     config.numAttrs = 1;
-    check(cudaLaunchKernelEx(&config, w8a8_tcgen05_prefill_pair<F>, map_w, map_x, args), "quantized pair GEMM launch");
+    // Up to 4096 output channels the tile runs with the tokens as MMA rows (epilogue straight from registers).
+    if (args.n <= 4096)
+        check(cudaLaunchKernelEx(&config, w8a8_tcgen05_prefill_pair<F, true>, map_w, map_x, args), "quantized pair GEMM launch");
+    else
+        check(cudaLaunchKernelEx(&config, w8a8_tcgen05_prefill_pair<F, false>, map_w, map_x, args), "quantized pair GEMM launch");
 }
 
 // Persistent K-group kernel: one CTA per multiprocessor over 128x128 tiles.
@@ -194,6 +198,8 @@ template <Type F> void raise_limits() {
     check(cudaFuncSetAttribute(w8a8_tcgen05_prefill_grouped<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kGroupedSmem)),
           "cudaFuncSetAttribute(shared memory)");
     check(cudaFuncSetAttribute(w8a8_tcgen05_prefill_pair<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kPairSmem)),
+          "cudaFuncSetAttribute(shared memory)");
+    check(cudaFuncSetAttribute(w8a8_tcgen05_prefill_pair<F, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kPairSmem)),
           "cudaFuncSetAttribute(shared memory)");
     check(cudaFuncSetAttribute(w8a8_tcgen05_prefill<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kPrefillSmem)),
           "cudaFuncSetAttribute(shared memory)");
